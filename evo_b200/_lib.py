@@ -95,7 +95,9 @@ class WindowAttnParams(C.Structure):
                 ("out", C.c_void_p), ("ldo", C.c_int64), ("dtype", C.c_int),
                 ("B", C.c_int), ("Lq", C.c_int64), ("H", C.c_int), ("G", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("n_maps", C.c_int),
                 ("q_pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("keep_first", C.c_int64),
-                ("scale", C.c_float), ("lambda_", C.c_float), ("head_norm", C.c_int), ("norm_eps", C.c_float), ("out_scale", C.c_float), ("gate_per_head", C.c_int)]
+                ("scale", C.c_float), ("lambda_", C.c_float), ("head_norm", C.c_int), ("norm_eps", C.c_float), ("out_scale", C.c_float), ("gate_per_head", C.c_int),
+                ("softcap", C.c_float), ("sink", C.c_void_p), ("pool", C.c_int64), ("pool_k", C.c_void_p), ("pool_v", C.c_void_p),
+                ("pool_tok_stride", C.c_int64), ("pool_batch_stride", C.c_int64)]
 
 
 class BranchNormParams(C.Structure):
@@ -127,6 +129,46 @@ class LatentDecodeParams(C.Structure):
                 ("out", C.c_void_p), ("ldo", C.c_int64),
                 ("B", C.c_int), ("Lq", C.c_int64), ("H", C.c_int), ("dim", C.c_int), ("rot", C.c_int), ("rank", C.c_int), ("vdim", C.c_int),
                 ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("scale", C.c_float), ("dtype", C.c_int), ("max_keys", C.c_int64)]
+
+
+SUM_NORM_BRANCHES = 3
+
+
+class SumNormParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("y", C.c_void_p * SUM_NORM_BRANCHES), ("ldy", C.c_int64 * SUM_NORM_BRANCHES),
+                ("norm_w", C.c_void_p * SUM_NORM_BRANCHES), ("scale", C.c_float * SUM_NORM_BRANCHES), ("n_branches", C.c_int),
+                ("eps", C.c_float), ("out", C.c_void_p * 2), ("w", C.c_void_p * 2), ("ldo", C.c_int64),
+                ("dtype", C.c_int), ("rows", C.c_int64), ("D", C.c_int), ("gather", C.c_void_p)]
+
+
+class ConvActParams(C.Structure):
+    _fields_ = [("inp", C.c_void_p), ("ld", C.c_int64), ("weight", C.c_void_p), ("bias", C.c_void_p),
+                ("carry", C.c_void_p), ("zero_start", C.c_int), ("out", C.c_void_p), ("ldo", C.c_int64),
+                ("B", C.c_int), ("L", C.c_int64), ("C", C.c_int), ("taps", C.c_int), ("act", C.c_int), ("dtype", C.c_int)]
+
+
+class GatedDeltaParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ld", C.c_int64),
+                ("b", C.c_void_p), ("a", C.c_void_p), ("gate", C.c_void_p), ("ldz", C.c_int64),
+                ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("norm_w", C.c_void_p),
+                ("eps", C.c_float), ("unit_eps", C.c_float), ("q_scale", C.c_float),
+                ("state", C.c_void_p), ("zero_start", C.c_int), ("out", C.c_void_p), ("ldo", C.c_int64), ("dtype", C.c_int),
+                ("B", C.c_int), ("L", C.c_int64), ("H", C.c_int), ("G", C.c_int), ("dk", C.c_int), ("dv", C.c_int)]
+
+
+class SsdParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("Bm", C.c_void_p), ("Cm", C.c_void_p), ("ld", C.c_int64), ("dt", C.c_void_p), ("ld_dt", C.c_int64),
+                ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("D", C.c_void_p), ("state", C.c_void_p), ("zero_start", C.c_int),
+                ("y", C.c_void_p), ("dtype", C.c_int), ("B", C.c_int), ("L", C.c_int64), ("H", C.c_int), ("G", C.c_int), ("N", C.c_int), ("dv", C.c_int)]
+
+
+class QkPrepParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ld", C.c_int64),
+                ("q_bias", C.c_void_p), ("k_bias", C.c_void_p), ("v_bias", C.c_void_p),
+                ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("eps", C.c_float), ("freq", C.c_void_p), ("rot_dims", C.c_int),
+                ("cache", C.c_void_p), ("cache_row", C.c_int64), ("cache_batch_stride", C.c_int64),
+                ("B", C.c_int), ("L", C.c_int64), ("H", C.c_int), ("G", C.c_int), ("dk", C.c_int), ("dv", C.c_int),
+                ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("dtype", C.c_int)]
 
 
 # name -> (restype, argtypes); every symbol include/evo_b200.h declares
@@ -190,6 +232,14 @@ SIGNATURES = {
     "evo_gather_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "evo_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "evo_sum_norm": (C.c_int, [C.POINTER(SumNormParams), C.c_void_p]),
+    "evo_conv_act": (C.c_int, [C.POINTER(ConvActParams), C.c_void_p]),
+    "evo_xielu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
+    "evo_gated_group_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
+    "evo_gated_delta_fwd": (C.c_int, [C.POINTER(GatedDeltaParams), C.c_void_p]),
+    "evo_ssd_fwd": (C.c_int, [C.POINTER(SsdParams), C.c_void_p]),
+    "evo_qk_prep": (C.c_int, [C.POINTER(QkPrepParams), C.c_void_p]),
+    "evo_pool_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),
     "evo_moe_route": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
 }
 

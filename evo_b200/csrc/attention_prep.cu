@@ -1,0 +1,128 @@
+// Preparation of attention inputs whose query and key are normed over the whole projection and rotated in part (evo_qk_prep), and
+// the pooled rows of a key/value cache (evo_pool_rows): the mean of every completed block of consecutive cache rows.
+// Biases, sums of squares, norms, angles and rotations are fp32; results are rounded once, when they are stored.
+#include "common.cuh"
+#include "../../include/evo_b200.h"
+#include <math.h>
+
+using namespace evo;
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// one CTA per row: the biased q and k rows wait in shared memory for their sums of squares, then are normed, turned and stored
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prep_kernel(evo_qk_prep_params p) {
+  extern __shared__ float sm[];
+  const int qw = p.H * p.dk, kw = p.G * p.dk, vw = p.G * p.dv;
+  float* qs = sm;              // [qw]
+  float* ks = qs + qw;         // [kw]
+  float* red = ks + kw;        // [33]
+  const int64_t row = blockIdx.x;
+  const int b = (int)(row / p.L);
+  const int64_t t = row - (int64_t)b * p.L;
+  const int64_t pos = (p.pos_dev ? *p.pos_dev : p.pos0) + t;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  T* q = (T*)p.q + row * p.ld;
+  const T* k = (const T*)p.k + row * p.ld;
+  const T* v = (const T*)p.v + row * p.ld;
+  T* crow = (T*)p.cache + (int64_t)b * p.cache_batch_stride + pos * p.cache_row;
+  const bf16* qb = (const bf16*)p.q_bias; const bf16* kb = (const bf16*)p.k_bias; const bf16* vb = (const bf16*)p.v_bias;
+  float sq = 0.f, sk = 0.f;
+  for (int c = tid; c < qw; c += nt) { const float x = ldf(q + c) + (qb ? __bfloat162float(qb[c]) : 0.f); qs[c] = x; sq = fmaf(x, x, sq); }
+  for (int c = tid; c < kw; c += nt) { const float x = ldf(k + c) + (kb ? __bfloat162float(kb[c]) : 0.f); ks[c] = x; sk = fmaf(x, x, sk); }
+  for (int c = tid; c < vw; c += nt) stf(crow + kw + c, ldf(v + c) + (vb ? __bfloat162float(vb[c]) : 0.f));
+  const float rq = p.q_norm_w ? 1.0f / sqrtf(block_sum(sq, red) / (float)qw + p.eps) : 1.f;
+  const float rk = p.k_norm_w ? 1.0f / sqrtf(block_sum(sk, red) / (float)kw + p.eps) : 1.f;
+  const bf16* qn = (const bf16*)p.q_norm_w; const bf16* kn = (const bf16*)p.k_norm_w;
+  const int half = p.rot_dims / 2;
+  // an entry is written by the thread that owns it; a turned pair (e, e + half) is owned by the thread of e
+  for (int part = 0; part < 2; ++part) {
+    const int width = part == 0 ? qw : kw;
+    const float* src = part == 0 ? qs : ks;
+    const bf16* nw = part == 0 ? qn : kn;
+    const float rs = part == 0 ? rq : rk;
+    T* dst = part == 0 ? q : crow;
+    for (int c = tid; c < width; c += nt) {
+      const int e = c % p.dk;
+      if (e >= p.rot_dims) { stf(dst + c, src[c] * rs * (nw ? __bfloat162float(nw[c]) : 1.f)); continue; }
+      if (e >= half) continue;
+      const float u = src[c] * rs * (nw ? __bfloat162float(nw[c]) : 1.f);
+      const float w = src[c + half] * rs * (nw ? __bfloat162float(nw[c + half]) : 1.f);
+      float sn, cs;
+      sincosf((float)pos * p.freq[e], &sn, &cs);
+      stf(dst + c, u * cs - w * sn);
+      stf(dst + c + half, w * cs + u * sn);
+    }
+  }
+}
+
+// grid (block slot, sequence): slot s is block pos / pool + s, done here iff its last row lies in [pos, pos + L)
+template <typename T>
+__global__ void __launch_bounds__(128) pool_rows_kernel(const T* __restrict__ cache, int64_t cache_row, int64_t cache_batch_stride, T* __restrict__ pooled,
+                                                        int64_t pooled_row, int64_t pooled_batch_stride, int64_t L, int width, int64_t pool,
+                                                        int64_t pos0, const int64_t* pos_dev) {
+  const int64_t pos = pos_dev ? *pos_dev : pos0;
+  const int64_t blk = pos / pool + blockIdx.x;
+  const int64_t last = blk * pool + pool - 1;
+  if (last < pos || last >= pos + L) return;
+  const int b = blockIdx.y;
+  const T* src = cache + (int64_t)b * cache_batch_stride + blk * pool * cache_row;
+  T* dst = pooled + (int64_t)b * pooled_batch_stride + blk * pooled_row;
+  const float inv = 1.0f / (float)pool;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float s = 0.f;
+    for (int64_t r = 0; r < pool; ++r) s += ldf(src + r * cache_row + c);
+    stf(dst + c, s * inv);
+  }
+}
+
+}  // namespace
+
+extern "C" int evo_qk_prep(const evo_qk_prep_params* p, void* stream) {
+  EVO_REQUIRE(p->q && p->k && p->v && p->cache, "evo_qk_prep: null argument");
+  EVO_REQUIRE(p->B >= 0 && p->L >= 0 && p->H > 0 && p->G > 0 && p->dk > 0 && p->dv > 0, "evo_qk_prep: bad shape");
+  EVO_REQUIRE(p->rot_dims >= 0 && p->rot_dims <= p->dk && p->rot_dims % 2 == 0 && (p->rot_dims == 0 || p->freq), "evo_qk_prep: bad rotation (%d of %d)", p->rot_dims, p->dk);
+  EVO_REQUIRE(p->cache_row >= (int64_t)p->G * (p->dk + p->dv), "evo_qk_prep: cache row too narrow");
+  if (p->B == 0 || p->L == 0) return 0;
+  const size_t smem = sizeof(float) * ((size_t)(p->H + p->G) * p->dk + 33);
+  EVO_REQUIRE(smem <= 200 * 1024, "evo_qk_prep: projections too wide for one CTA's shared memory");
+  auto kern = p->dtype ? qk_prep_kernel<float> : qk_prep_kernel<bf16>;
+  if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<(unsigned)((int64_t)p->B * p->L), 256, smem, (cudaStream_t)stream>>>(*p);
+  return check_launch("evo_qk_prep");
+}
+
+extern "C" int evo_pool_rows(const void* cache, int64_t cache_row, int64_t cache_batch_stride, void* pooled, int64_t pooled_row, int64_t pooled_batch_stride,
+                             int B, int64_t L, int width, int64_t pool, int64_t pos0, const int64_t* pos_dev, int dtype, void* stream) {
+  EVO_REQUIRE(cache && pooled && pool > 0 && width > 0 && B >= 0 && L >= 0, "evo_pool_rows: bad arguments");
+  if (B == 0 || L == 0) return 0;
+  const dim3 grid((unsigned)(L / pool + 2), B);       // blocks that can end inside any L consecutive positions
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype) pool_rows_kernel<float><<<grid, 128, 0, st>>>((const float*)cache, cache_row, cache_batch_stride, (float*)pooled, pooled_row, pooled_batch_stride, L, width, pool, pos0, pos_dev);
+  else pool_rows_kernel<bf16><<<grid, 128, 0, st>>>((const bf16*)cache, cache_row, cache_batch_stride, (bf16*)pooled, pooled_row, pooled_batch_stride, L, width, pool, pos0, pos_dev);
+  return check_launch("evo_pool_rows");
+}

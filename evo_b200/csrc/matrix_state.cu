@@ -1,0 +1,246 @@
+// Recurrences whose state is a (dk x dv) matrix per head, carried in fp32 registers for the whole call:
+//   gated delta rule   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q        (evo_gated_delta_fwd)
+//   state-space dual   S <- a S + (dt B) x^T;  y = S^T C + D x                             (evo_ssd_fwd)
+// with everything around them that the recurrence consumes computed here in fp32 from the activated projections: the unit norms of
+// q and k, sigmoid / softplus / exponentials of the per-head gates, and for the delta rule the head's RMS norm, weight and SiLU gate.
+//
+// One CTA per (head, sequence).  Column j of the state belongs to LPC adjacent lanes of one warp, each holding RPT rows
+// (lane l: rows l*RPT .. l*RPT+RPT); column sums (S^T k, S^T q) are folded with shuffles, so the time loop has no barrier.
+// TCH tokens are staged per round in shared memory: (k, q) pairs per state row, values, and the per-token numbers.
+// The delta rule needs S^T k before it can write: both products are taken from the decayed state in one pass,
+//   p = (gS)^T k,  r = (gS)^T q,  u = beta (v - p),  o = r + u (k . q),
+// and the rank-one update follows with u -- one shuffle fold per token instead of two.
+// The single-token step is the same kernel with L == 1.
+#include "common.cuh"
+#include "../../include/evo_b200.h"
+#include <math.h>
+
+using namespace evo;
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+constexpr int TCH = 16;      // tokens staged per round
+enum { MODE_DELTA = 0, MODE_SSD = 1 };
+
+// what both recurrences look like to the time loop
+struct ScanArgs {
+  const void* kk; const void* qq; const void* vv; int64_t ld;      // "key" (G*dk), "query" (G*dk), "value" (H*dv) columns of the activated rows
+  const void* s0; const void* s1; int64_t lds;                     // per-head raw numbers: delta (b, a), ssd (dt, -)
+  const void* A_log; const void* dt_bias; const void* Dskip;
+  float unit_eps, q_scale;
+  float* state; int zero_start;
+  // delta epilogue
+  const void* gate; int64_t ldg; const void* norm_w; float eps; void* out; int64_t ldo;
+  // ssd output
+  float* y;
+  int B; int64_t L; int H, G, dk, dv;
+};
+
+template <typename T, int RPT, int MODE>
+__global__ void __launch_bounds__(RPT <= 32 ? 1024 : 512, 1) matrix_state_kernel(ScanArgs p, int LPC, int dvp) {
+  extern __shared__ __align__(16) float smem[];
+  const int dk = p.dk, dv = p.dv, dkp = LPC * RPT;
+  float2* kq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]   (key, query) per state row
+  float* vs = smem + 2 * TCH * dkp;                        // [TCH][dvp]
+  float* sc = vs + TCH * dvp;                              // [TCH][4]     delta: (g, beta, k.q, -)   ssd: (a, D, -, -)
+  float* os = sc + TCH * 4;                                // [TCH][dvp]   delta read-outs
+  const int h = blockIdx.x, b = blockIdx.y, g = h / (p.H / p.G);
+  const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nw = nthr >> 5;
+  const int j = tid / LPC, l = tid % LPC;
+  const bool live = j < dv;
+  const T* kp = (const T*)p.kk + (int64_t)g * dk;
+  const T* qp = (const T*)p.qq + (int64_t)g * dk;
+  const T* vp = (const T*)p.vv + (int64_t)h * dv;
+  float* Sg = p.state ? p.state + ((int64_t)b * p.H + h) * dk * (int64_t)dv : nullptr;
+  const float A = expf(__bfloat162float(((const bf16*)p.A_log)[h]));
+  const float dtb = __bfloat162float(((const bf16*)p.dt_bias)[h]);
+  const float Dh = MODE == MODE_SSD ? __bfloat162float(((const bf16*)p.Dskip)[h]) : 0.f;
+
+  float S[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    const int k = l * RPT + r;
+    S[r] = (Sg && !p.zero_start && live && k < dk) ? Sg[(int64_t)k * dv + j] : 0.f;
+  }
+
+  for (int64_t t0 = 0; t0 < p.L; t0 += TCH) {
+    const int nt = (int)min((int64_t)TCH, p.L - t0);
+    const int64_t row0 = (int64_t)b * p.L + t0;
+    __syncthreads();                                   // the previous round's staging and read-outs are no longer read
+    // ---- staging: one warp per token
+    for (int tt = warp; tt < nt; tt += nw) {
+      const int64_t row = row0 + tt;
+      if (MODE == MODE_DELTA) {
+        float sk = 0.f, sq = 0.f, skq = 0.f;
+        for (int e = lane; e < dk; e += 32) {
+          const float kv = ldf(kp + row * p.ld + e), qv = ldf(qp + row * p.ld + e);
+          sk = fmaf(kv, kv, sk); sq = fmaf(qv, qv, sq); skq = fmaf(kv, qv, skq);
+        }
+        sk = warp_sum(sk); sq = warp_sum(sq); skq = warp_sum(skq);
+        const float rk = 1.0f / sqrtf(sk + p.unit_eps), rq = p.q_scale / sqrtf(sq + p.unit_eps);
+        for (int e = lane; e < dkp; e += 32) {
+          float2 o = make_float2(0.f, 0.f);
+          if (e < dk) { o.x = ldf(kp + row * p.ld + e) * rk; o.y = ldf(qp + row * p.ld + e) * rq; }
+          kq[tt * dkp + e] = o;
+        }
+        if (lane == 0) {
+          const float bv = ldf((const T*)p.s0 + row * p.lds + h), av = ldf((const T*)p.s1 + row * p.lds + h);
+          sc[tt * 4 + 0] = expf(-A * softplus_f(av + dtb));
+          sc[tt * 4 + 1] = 1.f / (1.f + expf(-bv));
+          sc[tt * 4 + 2] = skq * rk * rq;
+        }
+      } else {
+        const float dt = softplus_f(ldf((const T*)p.s0 + row * p.lds + h) + dtb);
+        for (int e = lane; e < dkp; e += 32) {
+          float2 o = make_float2(0.f, 0.f);
+          if (e < dk) { o.x = ldf(kp + row * p.ld + e) * dt; o.y = ldf(qp + row * p.ld + e); }
+          kq[tt * dkp + e] = o;
+        }
+        if (lane == 0) { sc[tt * 4 + 0] = expf(-A * dt); sc[tt * 4 + 1] = Dh; }
+      }
+      for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = c < dv ? ldf(vp + row * p.ld + c) : 0.f;
+    }
+    __syncthreads();
+    // ---- time loop
+    for (int tt = 0; tt < nt; ++tt) {
+      const float v = vs[tt * dvp + j];
+      const float dec = sc[tt * 4 + 0];
+      const float4* e = reinterpret_cast<const float4*>(kq + tt * dkp + l * RPT);       // two state rows per 16-byte read
+      if (MODE == MODE_DELTA) {
+        float pk = 0.f, pq = 0.f;
+#pragma unroll
+        for (int r = 0; r < RPT / 2; ++r) {
+          const float4 f = e[r];
+          S[2 * r] *= dec;          pk = fmaf(S[2 * r], f.x, pk);     pq = fmaf(S[2 * r], f.y, pq);
+          S[2 * r + 1] *= dec;      pk = fmaf(S[2 * r + 1], f.z, pk); pq = fmaf(S[2 * r + 1], f.w, pq);
+        }
+        for (int o = 1; o < LPC; o <<= 1) { pk += __shfl_xor_sync(0xffffffffu, pk, o); pq += __shfl_xor_sync(0xffffffffu, pq, o); }
+        const float u = sc[tt * 4 + 1] * (v - pk);
+#pragma unroll
+        for (int r = 0; r < RPT / 2; ++r) {
+          const float4 f = e[r];
+          S[2 * r] = fmaf(f.x, u, S[2 * r]);
+          S[2 * r + 1] = fmaf(f.z, u, S[2 * r + 1]);
+        }
+        if (l == 0) os[tt * dvp + j] = fmaf(u, sc[tt * 4 + 2], pq);
+      } else {
+        float y = 0.f;
+#pragma unroll
+        for (int r = 0; r < RPT / 2; ++r) {
+          const float4 f = e[r];
+          S[2 * r] = fmaf(dec, S[2 * r], f.x * v);          y = fmaf(S[2 * r], f.y, y);
+          S[2 * r + 1] = fmaf(dec, S[2 * r + 1], f.z * v);  y = fmaf(S[2 * r + 1], f.w, y);
+        }
+        for (int o = 1; o < LPC; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+        if (l == 0 && live) p.y[((row0 + tt) * p.H + h) * dv + j] = fmaf(sc[tt * 4 + 1], v, y);
+      }
+    }
+    if (MODE == MODE_DELTA) {
+      __syncthreads();
+      // head norm, weight, SiLU gate, store: one warp per token
+      const bf16* nwt = (const bf16*)p.norm_w;
+      for (int tt = warp; tt < nt; tt += nw) {
+        const int64_t row = row0 + tt;
+        float ss = 0.f;
+        for (int c = lane; c < dv; c += 32) { const float o = os[tt * dvp + c]; ss = fmaf(o, o, ss); }
+        ss = warp_sum(ss);
+        const float rstd = 1.0f / sqrtf(ss / (float)dv + p.eps);
+        T* orow = (T*)p.out + row * p.ldo;
+        const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * dv;
+        for (int c = lane; c < dv; c += 32) {
+          const float gv = ldf(grow + c);
+          stf(orow + h * dv + c, os[tt * dvp + c] * rstd * __bfloat162float(nwt[c]) * (gv / (1.f + expf(-gv))));
+        }
+        if (h == p.H - 1)
+          for (int64_t c = (int64_t)p.H * dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+      }
+    }
+  }
+  if (Sg && live) {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const int k = l * RPT + r;
+      if (k < dk) Sg[(int64_t)k * dv + j] = S[r];
+    }
+  }
+}
+
+struct Plan { int rpt, lpc, dvp; };
+// LPC (a power of two <= 32) lanes per column with RPT rows each; fewest rows per thread that keep the CTA within 1024 threads
+inline Plan plan(int dk, int dv) {
+  const int dvp = (dv + 31) / 32 * 32;      // (dvp * LPC) is then a multiple of 32 and a column never straddles two warps
+  for (int rpt : {4, 8, 16, 32, 64}) {
+    int lpc = 1;
+    while (lpc * rpt < dk) lpc <<= 1;
+    if (lpc <= 32 && (int64_t)lpc * dvp <= (rpt <= 32 ? 1024 : 512)) return {rpt, lpc, dvp};
+  }
+  return {0, 0, 0};
+}
+
+template <typename T, int RPT, int MODE>
+int launch(const ScanArgs& a, const Plan& pl, cudaStream_t st, const char* what) {
+  const size_t smem = sizeof(float) * ((size_t)2 * TCH * pl.lpc * RPT + (size_t)2 * TCH * pl.dvp + (size_t)TCH * 4);
+  auto kern = matrix_state_kernel<T, RPT, MODE>;
+  if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<dim3(a.H, a.B), dim3(pl.lpc * pl.dvp), smem, st>>>(a, pl.lpc, pl.dvp);
+  return check_launch(what);
+}
+
+template <typename T, int MODE>
+int dispatch(const ScanArgs& a, cudaStream_t st, const char* what) {
+  const Plan pl = plan(a.dk, a.dv);
+  if (pl.rpt == 0) { set_error("%s: a state of %d x %d per head does not fit one CTA (rows <= 2048, value channels <= 512)", what, a.dk, a.dv); return -1; }
+  switch (pl.rpt) {
+    case 4: return launch<T, 4, MODE>(a, pl, st, what);
+    case 8: return launch<T, 8, MODE>(a, pl, st, what);
+    case 16: return launch<T, 16, MODE>(a, pl, st, what);
+    case 32: return launch<T, 32, MODE>(a, pl, st, what);
+    default: return launch<T, 64, MODE>(a, pl, st, what);
+  }
+}
+
+}  // namespace
+
+extern "C" int evo_gated_delta_fwd(const evo_gated_delta_params* p, void* stream) {
+  EVO_REQUIRE(p->q && p->k && p->v && p->b && p->a && p->gate && p->A_log && p->dt_bias && p->norm_w && p->out, "evo_gated_delta_fwd: null argument");
+  EVO_REQUIRE(p->B >= 0 && p->L >= 0 && p->H > 0 && p->G > 0 && p->H % p->G == 0 && p->dk > 0 && p->dv > 0 && p->ldo >= (int64_t)p->H * p->dv,
+              "evo_gated_delta_fwd: bad shape");
+  if (p->B == 0 || p->L == 0) return 0;
+  ScanArgs a = {};
+  a.kk = p->k; a.qq = p->q; a.vv = p->v; a.ld = p->ld;
+  a.s0 = p->b; a.s1 = p->a; a.lds = p->ldz;
+  a.A_log = p->A_log; a.dt_bias = p->dt_bias;
+  a.unit_eps = p->unit_eps; a.q_scale = p->q_scale;
+  a.state = p->state; a.zero_start = p->zero_start;
+  a.gate = p->gate; a.ldg = p->ldz; a.norm_w = p->norm_w; a.eps = p->eps; a.out = p->out; a.ldo = p->ldo;
+  a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->G; a.dk = p->dk; a.dv = p->dv;
+  return p->dtype ? dispatch<float, MODE_DELTA>(a, (cudaStream_t)stream, "evo_gated_delta_fwd") : dispatch<bf16, MODE_DELTA>(a, (cudaStream_t)stream, "evo_gated_delta_fwd");
+}
+
+extern "C" int evo_ssd_fwd(const evo_ssd_params* p, void* stream) {
+  EVO_REQUIRE(p->x && p->Bm && p->Cm && p->dt && p->A_log && p->dt_bias && p->D && p->y, "evo_ssd_fwd: null argument");
+  EVO_REQUIRE(p->B >= 0 && p->L >= 0 && p->H > 0 && p->G > 0 && p->H % p->G == 0 && p->N > 0 && p->dv > 0, "evo_ssd_fwd: bad shape");
+  if (p->B == 0 || p->L == 0) return 0;
+  ScanArgs a = {};
+  a.kk = p->Bm; a.qq = p->Cm; a.vv = p->x; a.ld = p->ld;
+  a.s0 = p->dt; a.lds = p->ld_dt;
+  a.A_log = p->A_log; a.dt_bias = p->dt_bias; a.Dskip = p->D;
+  a.state = p->state; a.zero_start = p->zero_start;
+  a.y = p->y;
+  a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->G; a.dk = p->N; a.dv = p->dv;
+  return p->dtype ? dispatch<float, MODE_SSD>(a, (cudaStream_t)stream, "evo_ssd_fwd") : dispatch<bf16, MODE_SSD>(a, (cudaStream_t)stream, "evo_ssd_fwd");
+}

@@ -1,6 +1,7 @@
 // Softmax attention over a linear key/value cache with (a) a sliding window that also keeps the first tokens of the
 // sequence, (b) one or two score maps per head over the same values (differential attention: o = a1 - lambda * a2),
-// (c) an optional per-head RMS norm without weight and (d) an optional sigmoid output gate -- one fused kernel; the
+// (c) an optional per-head RMS norm without weight, (d) an optional sigmoid output gate, (e) optionally soft-capped scores, a learned
+// sink in the softmax denominator and, before the window, one pooled key/value per block of tokens -- one fused kernel; the
 // scores, the softmax weights, the combination of the maps and the head norm are fp32 whatever the activation type.
 //
 // Work per query is bounded by window + keep_first keys, so the kernel is a CUDA-core streaming-softmax kernel: one warp
@@ -63,6 +64,14 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// soft cap of a scaled score: cap * tanh(s / cap), off when cap <= 0
+__device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// pooled blocks that position i sees: those that end at or before i - window
+__device__ __forceinline__ int64_t blocks_seen(int64_t i, int64_t window, int64_t pool) {
+  const int64_t n = i - window + 1;
+  return (pool > 0 && window > 0 && n > 0) ? n / pool : 0;
+}
+
 template <int NM, int MAXCV>      // MAXCV: value channels per lane (dv <= 32 * MAXCV)
 struct Softmax {
   float m[NM], l[NM], acc[NM][MAXCV];
@@ -78,13 +87,13 @@ struct Softmax {
 
 // scores of this lane's key for all maps -> running max / sum update; returns the lane's probabilities in pm
 template <int NM, int MAXCV>
-__device__ __forceinline__ bool tile_scores(Softmax<NM, MAXCV>& sm, const float* qrow, const float* krow, int dk, float scale, bool vis, float* pm) {
+__device__ __forceinline__ bool tile_scores(Softmax<NM, MAXCV>& sm, const float* qrow, const float* krow, int dk, float scale, float cap, bool vis, float* pm) {
   float s[NM];
 #pragma unroll
   for (int a = 0; a < NM; ++a) {
     float d = 0.f;
     for (int e = 0; e < dk; ++e) d = fmaf(qrow[a * dk + e], krow[a * dk + e], d);
-    s[a] = vis ? d * scale : -INFINITY;
+    s[a] = vis ? capped(d * scale, cap) : -INFINITY;
   }
   if (!__any_sync(0xffffffffu, vis)) return false;
 #pragma unroll
@@ -107,10 +116,22 @@ __device__ __forceinline__ void finish_row(const evo_window_attn_params& p, cons
   const int dv = p.dv;
   float o[MAXCV];
   float ss = 0.f;
+  // a sink adds exp(sink_h) to the denominator: with mx = max(m, sink), acc / l becomes acc e^(m-mx) / (l e^(m-mx) + e^(sink-mx))
+  float num[NM], den[NM];
+#pragma unroll
+  for (int a = 0; a < NM; ++a) {
+    num[a] = 1.f; den[a] = sm.l[a];
+    if (p.sink) {
+      const float sk = __bfloat162float(((const bf16*)p.sink)[h]);
+      const float mx = fmaxf(sm.m[a], sk);
+      num[a] = expf(sm.m[a] - mx);
+      den[a] = fmaf(sm.l[a], num[a], expf(sk - mx));
+    }
+  }
 #pragma unroll
   for (int c = 0; c < MAXCV; ++c) {
-    float v = sm.acc[0][c] / sm.l[0];
-    if (NM == 2) v -= p.lambda * (sm.acc[NM - 1][c] / sm.l[NM - 1]);
+    float v = sm.acc[0][c] * num[0] / den[0];
+    if (NM == 2) v -= p.lambda * (sm.acc[NM - 1][c] * num[NM - 1] / den[NM - 1]);
     o[c] = ((BLOCKED ? lane * MAXCV + c : lane + 32 * c) < dv) ? v : 0.f;
     ss = fmaf(o[c], o[c], ss);
   }
@@ -158,28 +179,35 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
   const bool windowed = p.window > 0;
   const int64_t win_lo = windowed ? max((int64_t)0, i_lo - p.window + 1) : 0;
   const int64_t keep_hi = windowed ? min(p.keep_first, win_lo) : 0;
+  const int64_t pool_hi = blocks_seen(i_hi, p.window, p.pool);          // pooled rows any query of this CTA sees
+  const int64_t my_blocks = blocks_seen(i, p.window, p.pool);
+  const T* pkb = pool_hi ? (const T*)p.pool_k + (int64_t)b * p.pool_batch_stride + (int64_t)g * kw : nullptr;
+  const T* pvb = pool_hi ? (const T*)p.pool_v + (int64_t)b * p.pool_batch_stride + (int64_t)g * dv : nullptr;
 
   Softmax<NM, MAXCV> sm;
   sm.init();
-  for (int part = 0; part < 2; ++part) {
-    const int64_t lo = part == 0 ? 0 : win_lo, hi = part == 0 ? keep_hi : i_hi + 1;       // keys [lo, hi)
+  for (int part = 0; part < 3; ++part) {                  // kept first tokens, pooled blocks, window
+    const int64_t lo = part == 2 ? win_lo : 0, hi = part == 0 ? keep_hi : (part == 1 ? pool_hi : i_hi + 1);       // rows [lo, hi)
+    const T* kbase = part == 1 ? pkb : kb;
+    const T* vbase = part == 1 ? pvb : vb;
+    const int64_t kstr = part == 1 ? p.pool_tok_stride : p.k_tok_stride, vstr = part == 1 ? p.pool_tok_stride : p.v_tok_stride;
     for (int64_t k0 = lo; k0 < hi; k0 += KT) {
       const int nk = (int)min((int64_t)KT, hi - k0);
       __syncthreads();
       for (int idx = threadIdx.x; idx < nk * kw; idx += QT * 32) {
         const int r = idx / kw, e = idx % kw;
-        Ks[r * kst + e] = ldf(kb + (k0 + r) * p.k_tok_stride + e);
+        Ks[r * kst + e] = ldf(kbase + (k0 + r) * kstr + e);
       }
       for (int idx = threadIdx.x; idx < nk * dv; idx += QT * 32) {
         const int r = idx / dv, e = idx % dv;
-        Vs[r * dv + e] = ldf(vb + (k0 + r) * p.v_tok_stride + e);
+        Vs[r * dv + e] = ldf(vbase + (k0 + r) * vstr + e);
       }
       __syncthreads();
       if (!valid) continue;
       const int64_t kj = k0 + lane;
-      const bool vis = lane < nk && kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first);
+      const bool vis = lane < nk && (part == 1 ? kj < my_blocks : (kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first)));
       float pm[NM];
-      if (!tile_scores<NM, MAXCV>(sm, Qs + w * kw, Ks + (lane < nk ? lane : 0) * kst, dk, p.scale, vis, pm)) continue;
+      if (!tile_scores<NM, MAXCV>(sm, Qs + w * kw, Ks + (lane < nk ? lane : 0) * kst, dk, p.scale, p.softcap, vis, pm)) continue;
       for (int r = 0; r < nk; ++r) {
         float pr[NM];
 #pragma unroll
@@ -222,15 +250,21 @@ __global__ void __launch_bounds__(QS_MAX * 32) window_attn_split_kernel(evo_wind
   const int64_t win_lo = windowed ? max((int64_t)0, i - p.window + 1) : 0;
   const int64_t keep_hi = windowed ? min(p.keep_first, win_lo) : 0;
   const int64_t n_keep = (keep_hi + KT - 1) / KT, n_win = (i + 1 - win_lo + KT - 1) / KT;
+  const int64_t pool_hi = blocks_seen(i, p.window, p.pool), n_pool = (pool_hi + KT - 1) / KT;
+  const T* pkb = pool_hi ? (const T*)p.pool_k + (int64_t)b * p.pool_batch_stride + (int64_t)g * kw : nullptr;
+  const T* pvb = pool_hi ? (const T*)p.pool_v + (int64_t)b * p.pool_batch_stride + (int64_t)g * dv : nullptr;
 
   Softmax<NM, MAXCV> sm;
   sm.init();
-  for (int64_t t = w; t < n_keep + n_win; t += nw) {
-    const int64_t k0 = t < n_keep ? t * KT : win_lo + (t - n_keep) * KT;
-    const int64_t hi = t < n_keep ? keep_hi : i + 1;
+  for (int64_t t = w; t < n_keep + n_pool + n_win; t += nw) {
+    const bool pooled = t >= n_keep && t < n_keep + n_pool;
+    const int64_t k0 = t < n_keep ? t * KT : (pooled ? (t - n_keep) * KT : win_lo + (t - n_keep - n_pool) * KT);
+    const int64_t hi = t < n_keep ? keep_hi : (pooled ? pool_hi : i + 1);
     const int nk = (int)min((int64_t)KT, hi - k0);
     const bool vis = lane < nk;                        // every key of these ranges is visible to the one query
-    const T* krow = kb + (k0 + (vis ? lane : 0)) * p.k_tok_stride;
+    const int64_t kstr = pooled ? p.pool_tok_stride : p.k_tok_stride, vstr = pooled ? p.pool_tok_stride : p.v_tok_stride;
+    const T* vsrc = pooled ? pvb : vb;
+    const T* krow = (pooled ? pkb : kb) + (k0 + (vis ? lane : 0)) * kstr;
     float s[NM], pm[NM];
 #pragma unroll
     for (int a = 0; a < NM; ++a) {
@@ -247,7 +281,7 @@ __global__ void __launch_bounds__(QS_MAX * 32) window_attn_split_kernel(evo_wind
       } else {
         for (int e = 0; e < dk; ++e) d = fmaf(Qs[a * dk + e], ldf(krow + a * dk + e), d);
       }
-      s[a] = vis ? d * p.scale : -INFINITY;
+      s[a] = vis ? capped(d * p.scale, p.softcap) : -INFINITY;
     }
 #pragma unroll
     for (int a = 0; a < NM; ++a) {
@@ -266,7 +300,7 @@ __global__ void __launch_bounds__(QS_MAX * 32) window_attn_split_kernel(evo_wind
         float pr[NM];
 #pragma unroll
         for (int a = 0; a < NM; ++a) pr[a] = __shfl_sync(0xffffffffu, pm[a], r);
-        const T* vrow = vb + (k0 + r) * p.v_tok_stride + lane * MAXCV;
+        const T* vrow = vsrc + (k0 + r) * vstr + lane * MAXCV;
 #pragma unroll
         for (int c = 0; c < MAXCV; c += 4) {
           if (mine && lane * MAXCV + c < dv) {
@@ -285,7 +319,7 @@ __global__ void __launch_bounds__(QS_MAX * 32) window_attn_split_kernel(evo_wind
       float pr[NM];
 #pragma unroll
       for (int a = 0; a < NM; ++a) pr[a] = __shfl_sync(0xffffffffu, pm[a], r);
-      const T* vrow = vb + (k0 + r) * p.v_tok_stride;
+      const T* vrow = vsrc + (k0 + r) * vstr;
 #pragma unroll
       for (int c = 0; c < MAXCV; ++c) {
         const int ch = lane + 32 * c;
@@ -332,13 +366,15 @@ int launch_cv(const evo_window_attn_params* p, cudaStream_t st) {
   if (p->Lq <= 4) {
     // the warps of a CTA take the query's key tiles in turn; each tile is a chain of dependent loads (keys -> weights -> values), so
     // a long window gets more warps: shorter chains and more bytes in flight
-    const int64_t span = p->window > 0 ? (int64_t)p->window + p->keep_first : (p->pos_dev ? (int64_t)1 << 30 : p->q_pos0 + p->Lq);
+    int64_t span = p->window > 0 ? (int64_t)p->window + p->keep_first : (p->pos_dev ? (int64_t)1 << 30 : p->q_pos0 + p->Lq);
+    if (p->pool > 0) span += p->pos_dev ? (int64_t)1 << 20 : (p->q_pos0 + p->Lq) / p->pool;
     const int warps = span >= 24 * KT ? QS_MAX : QT;
     const size_t smem = sizeof(float) * ((size_t)kw + (size_t)warps * NM * (2 + MAXCV * 32));
     constexpr int EV = Row16<T>::EV;
     auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
     const bool vec = p->dk % EV == 0 && p->dv % 4 == 0 && p->k_tok_stride % EV == 0 && p->k_batch_stride % EV == 0 && p->v_tok_stride % EV == 0 &&
-                     p->v_batch_stride % EV == 0 && a16(p->k) && a16(p->v);
+                     p->v_batch_stride % EV == 0 && a16(p->k) && a16(p->v) &&
+                     (p->pool <= 0 || (p->pool_tok_stride % EV == 0 && p->pool_batch_stride % EV == 0 && a16(p->pool_k) && a16(p->pool_v)));
     auto kern = vec ? window_attn_split_kernel<T, NM, MAXCV, true> : window_attn_split_kernel<T, NM, MAXCV, false>;
     if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<dim3((unsigned)p->Lq, p->H, p->B), warps * 32, smem, st>>>(*p);
@@ -367,6 +403,7 @@ extern "C" int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream
   EVO_REQUIRE(p->n_maps == 1 || p->n_maps == 2, "evo_window_attn_fwd: n_maps must be 1 or 2");
   EVO_REQUIRE(p->dv <= 512, "evo_window_attn_fwd: dv (%d) must be <= 512", p->dv);
   EVO_REQUIRE(p->ldo >= (int64_t)p->H * p->dv, "evo_window_attn_fwd: ldo too small");
+  EVO_REQUIRE(p->pool <= 0 || (p->window > 0 && p->pool_k && p->pool_v), "evo_window_attn_fwd: pooled blocks need a window and the pooled rows");
   if (p->B == 0 || p->Lq == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   static const char* env_mma = getenv("EVO_B200_WINDOW_ATTN_MMA");      // "0": always the CUDA-core kernel (comparisons)

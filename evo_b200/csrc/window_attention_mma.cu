@@ -290,5 +290,6 @@ int dispatch(const evo_window_attn_params* p, cudaStream_t st) {
 
 int evo::window_attn_mma(const evo_window_attn_params* p, cudaStream_t st) {
   if (p->dtype != 0 || p->dk * p->n_maps > 256 || p->dk > 128 || p->dv > 128 || p->dv % 8 != 0 || p->Lq < 16) return 1;
+  if (p->pool > 0 || p->sink || p->softcap > 0.f) return 1;      // pooled blocks, sink and soft cap: the CUDA-core kernels
   return p->n_maps == 2 ? dispatch<2>(p, st) : dispatch<1>(p, st);
 }

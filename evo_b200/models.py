@@ -125,6 +125,13 @@ def _load_movalorn(model_dir: str, config: dict, device, dtype, **kwargs):
     return _load_flat(family, model_dir, config, device, dtype)
 
 
+def _load_nelovik(model_dir: str, config: dict, device, dtype, **kwargs):
+    def family():
+        from .nelovik import Nelovik, NelovikConfig
+        return Nelovik, NelovikConfig
+    return _load_flat(family, model_dir, config, device, dtype)
+
+
 def _load_stripedhyena(model_dir: str, config: dict, device, dtype, model_name: str = "evo-1-8k-base", **kwargs):
     if dtype not in (None, torch.bfloat16):
         raise NotImplementedError("StripedHyena runs in bfloat16 (fp32 poles and residues) only")
@@ -135,6 +142,7 @@ def _load_stripedhyena(model_dir: str, config: dict, device, dtype, model_name: 
 ARCHITECTURES = {
     "Zaverax": (_load_zaverax, (torch.bfloat16, torch.float32)),
     "Movalorn": (_load_movalorn, (torch.bfloat16, torch.float32)),
+    "Nelovik": (_load_nelovik, (torch.bfloat16, torch.float32)),
     "StripedHyena": (_load_stripedhyena, (torch.bfloat16,)),
     "StripedHyenaModelForCausalLM": (_load_stripedhyena, (torch.bfloat16,)),
 }

@@ -139,6 +139,10 @@ class StreamDecoder(KernelOps, nn.Module):
             ip.max_seqlen = max(ip.max_seqlen, cache.shape[1])
         return cache
 
+    def _cache_tokens(self, key, cache) -> int:
+        """Tokens of a sequence that the cache under `key` has room for (a family that keeps one row per several tokens overrides this)."""
+        return cache.shape[1]
+
     # ---- kernels ---------------------------------------------------------------------------------
     @property
     def _dt(self) -> int:
@@ -197,9 +201,9 @@ class StreamDecoder(KernelOps, nn.Module):
         n_out = n_steps - n_forced if n_out is None else n_out
         if n_out < 0:
             raise ValueError("more forced tokens than steps")
-        for c in mha_ip.key_value_memory_dict.values():
-            if start_pos + n_steps > c.shape[1]:
-                raise _lib.EvoError(f"sequence length {start_pos + n_steps} exceeds the KV cache ({c.shape[1]})")
+        for k, c in mha_ip.key_value_memory_dict.items():
+            if start_pos + n_steps > self._cache_tokens(k, c):
+                raise _lib.EvoError(f"sequence length {start_pos + n_steps} exceeds the KV cache ({self._cache_tokens(k, c)})")
         with torch.cuda.device(dev), torch.no_grad():
             self._ensure_packed()
             picked = torch.empty(B, max(n_out, 1), dtype=torch.long, device=dev)

@@ -354,6 +354,16 @@ typedef struct {
   float scale, lambda;
   int head_norm; float norm_eps, out_scale;
   int gate_per_head;      /* 1: gate holds one number per head (column h), else one per output channel (column h*dv + c) */
+  /* optional extensions (all off when zero / NULL):
+   *   softcap > 0: score <- softcap * tanh(score * scale / softcap);
+   *   sink (H, bf16): exp(sink_h) joins every softmax denominator of head h (no key, no value, neither scaled nor capped);
+   *   pool > 0: besides its window, query i sees one pooled key/value per block of `pool` tokens that lies wholly before the
+   *   window, i.e. blocks b < (i - window + 1) / pool; pooled row b of a sequence is at pool_k/pool_v + batch * pool_batch_stride
+   *   + b * pool_tok_stride with the column layout of k / v (the caller keeps them: evo_pool_rows).  Tokens and blocks share one softmax. */
+  float softcap;
+  const void* sink;
+  int64_t pool;
+  const void* pool_k; const void* pool_v; int64_t pool_tok_stride, pool_batch_stride;
 } evo_window_attn_params;
 int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream);
 
@@ -461,6 +471,100 @@ int evo_moe_scatter(const int32_t* chosen, int64_t n, int top, int E, const int3
 int evo_gather_rows(const void* src, int64_t ld_src_bytes, void* dst, int64_t ld_dst_bytes, const int32_t* perm, int64_t rows, int64_t width_bytes, void* stream);
 int evo_moe_combine(const void* ys, int64_t ldy, const void* base, int64_t ldb, const float* weights, const int32_t* chosen, const int32_t* slot_of,
                     void* out, int64_t ldo, int64_t rows, int D, int E, int top, int dtype, void* stream);
+
+/* ==== designs whose layers run the mixer and the feed-forward side by side on two norms of the same stream, with matrix-state
+ * recurrences (gated delta rule, state-space duality) and a windowed attention over tokens and pooled blocks (Nelovik).
+ * Same conventions: `dtype` 0 = bf16 activations, 1 = fp32; weights and parameter vectors bf16. ==== */
+
+/* Closes a layer of up to EVO_SUM_NORM_BRANCHES parallel branches and opens the next one, one pass per row of the fp32 stream x (rows, D):
+ *   x <- x + sum_b scale[b] * (norm_w[b] ? y[b] / sqrt(mean(y[b]^2) + eps) * norm_w[b] : y[b])
+ *   out[n] = x / sqrt(mean(x^2) + eps) * w[n]      for the outputs that are given (n < 2), pad columns [D, ldo) zero.
+ * gather (rows) int64: row i reads stream row gather[i] (the branches are then added for the outputs only; x is not written back). */
+#define EVO_SUM_NORM_BRANCHES 3
+typedef struct {
+  float* x;
+  const void* y[EVO_SUM_NORM_BRANCHES]; int64_t ldy[EVO_SUM_NORM_BRANCHES];
+  const void* norm_w[EVO_SUM_NORM_BRANCHES]; float scale[EVO_SUM_NORM_BRANCHES];
+  int n_branches;
+  float eps;
+  void* out[2]; const void* w[2]; int64_t ldo;
+  int dtype;
+  int64_t rows; int D;
+  const int64_t* gather;
+} evo_sum_norm_params;
+int evo_sum_norm(const evo_sum_norm_params* p, void* stream);
+
+/* Short causal convolution over time per channel on columns of a projection, then an activation:
+ *   out[b,t,c] = act(bias[c] + sum_j weight[c,j] * in[b, t - (taps-1) + j, c]),  act 0 = none, 1 = silu;
+ * in (B*L, ld) rows, channel c at column c; weight (C, taps) bf16, the last column multiplies the current token; bias (C) bf16 optional.
+ * carry (B, taps-1, C) fp32 (optional) holds the inputs before this call's first token (zero_start: zeros) and receives the last taps-1 inputs. */
+typedef struct {
+  const void* in; int64_t ld;
+  const void* weight; const void* bias;
+  float* carry; int zero_start;
+  void* out; int64_t ldo;
+  int B; int64_t L; int C, taps, act, dtype;
+} evo_conv_act_params;
+int evo_conv_act(const evo_conv_act_params* p, void* stream);
+
+/* xIELU: out = softplus(p) z^2 + z/2 (z > 0), (1/2 + softplus(q)) (e^z - 1 - z) + z/2 (z <= 0); coef = (p, q) bf16; columns [F, ldo) zero. */
+int evo_xielu(const void* z, int64_t ldz, const void* coef, void* out, int64_t ldo, int64_t rows, int F, int dtype, void* stream);
+
+/* out = group_rms(y * silu(gate)) * norm_w: the row's `width` values are normed in `groups` equal parts, each by its own root mean
+ * square; y (rows, width) fp32, gate (rows, ldg) and out (rows, ldo) activations, columns [width, ldo) zero. */
+int evo_gated_group_norm(const float* y, const void* gate, int64_t ldg, const void* norm_w, void* out, int64_t ldo,
+                         int64_t rows, int width, int groups, float eps, int dtype, void* stream);
+
+/* Gated delta rule, per head h (key head h / (H/G)), over the activated projections q, k (G*dk), v (H*dv) of a row:
+ *   qn = q / sqrt(sum(q^2) + unit_eps) * q_scale,  kn = k / sqrt(sum(k^2) + unit_eps),
+ *   beta = sigmoid(b_h),  g = exp(-exp(A_log_h) * softplus(a_h + dt_bias_h)),
+ *   S <- g S;  u = beta (v - S^T kn);  S <- S + kn u^T;  o = S^T qn,
+ *   out = o / sqrt(mean(o^2) + eps) * norm_w * silu(gate)     over the head's dv values.
+ * S (B, H, dk, dv) fp32 is read (unless zero_start) and written back (unless NULL); everything after the inputs is fp32. */
+typedef struct {
+  const void* q; const void* k; const void* v; int64_t ld;         /* one buffer of activated projections, row stride ld */
+  const void* b; const void* a; const void* gate; int64_t ldz;    /* raw projections: (rows, H), (rows, H), (rows, H*dv), row stride ldz */
+  const void* A_log; const void* dt_bias; const void* norm_w;
+  float eps, unit_eps, q_scale;
+  float* state; int zero_start;
+  void* out; int64_t ldo; int dtype;
+  int B; int64_t L; int H, G, dk, dv;
+} evo_gated_delta_params;
+int evo_gated_delta_fwd(const evo_gated_delta_params* p, void* stream);
+
+/* State-space duality recurrence, per head h (group h / (H/G)), over the activated x (H*dv), Bm, Cm (G*N) of a row and the raw step dt (H):
+ *   d = softplus(dt_h + dt_bias_h),  S <- exp(-exp(A_log_h) d) S + d Bm x^T,  y = S^T Cm + D_h x     (S is N x dv, fp32).
+ * y (rows, H*dv) fp32.  S (B, H, N, dv) fp32 is read (unless zero_start) and written back (unless NULL). */
+typedef struct {
+  const void* x; const void* Bm; const void* Cm; int64_t ld;
+  const void* dt; int64_t ld_dt;
+  const void* A_log; const void* dt_bias; const void* D;
+  float* state; int zero_start;
+  float* y;
+  int dtype;
+  int B; int64_t L; int H, G, N, dv;
+} evo_ssd_params;
+int evo_ssd_fwd(const evo_ssd_params* p, void* stream);
+
+/* Preparation of attention projections whose query and key are normed over the WHOLE projection and partly rotated, one row at a time:
+ *   q <- rms(q + q_bias) * q_norm_w (over all H*dk entries), k likewise over G*dk, v <- v + v_bias;
+ *   in every head the first rot_dims entries turn by pos * freq[i], entry i paired with entry i + rot_dims/2 (i < rot_dims/2; freq fp32);
+ *   q is written back in place, [k | v] goes to the cache row of the token's position (pos = *pos_dev if given else pos0, plus its index). */
+typedef struct {
+  void* q; const void* k; const void* v; int64_t ld;                /* one projection buffer (rows, ld) */
+  const void* q_bias; const void* k_bias; const void* v_bias;     /* optional */
+  const void* q_norm_w; const void* k_norm_w; float eps;
+  const float* freq; int rot_dims;
+  void* cache; int64_t cache_row, cache_batch_stride;
+  int B; int64_t L; int H, G, dk, dv;
+  int64_t pos0; const int64_t* pos_dev; int dtype;
+} evo_qk_prep_params;
+int evo_qk_prep(const evo_qk_prep_params* p, void* stream);
+
+/* Pooled cache rows: for every block b of `pool` consecutive cache rows that this call completed (its last row bP + P - 1 lies in
+ * [pos, pos + L)), pooled row b = mean of the block's rows as the cache holds them (fp32 sum), `width` entries per row. */
+int evo_pool_rows(const void* cache, int64_t cache_row, int64_t cache_batch_stride, void* pooled, int64_t pooled_row, int64_t pooled_batch_stride,
+                  int B, int64_t L, int width, int64_t pool, int64_t pos0, const int64_t* pos_dev, int dtype, void* stream);
 
 #ifdef __cplusplus
 }
