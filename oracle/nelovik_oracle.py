@@ -193,3 +193,84 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
         if taps is not None:
             taps.append(x.clone())
     return (rms(x, eps) * W["final.norm"]) @ W["head"].T
+
+
+# ---- small configurations and random weights for the tests --------------------------------------------------------------
+def make_config(width=48, vocab=61, layers=("parallel", "delta", "delta_2"), ff=40, no_ff_layers=(), eps=1e-5,
+                heads=2, kv_heads=1, dim=8, vdim=12, taps=3,                                    # gated delta rule
+                att_heads=4, att_kv_heads=2, att_dim=12, att_vdim=10, window=9, pool=3, rot_dims=8, rot_base=100.0, scale=0.3, softcap=5.0,
+                ssd_heads=4, ssd_vdim=6, state=5, groups=2, norm_groups=3, ssd_taps=2) -> dict:
+    """A config.json dict; entries of `layers` may also be complete layer dicts (layers with sizes of their own)."""
+    out = []
+    for i, kind in enumerate(layers):
+        if isinstance(kind, dict):
+            out.append(kind)
+            continue
+        if kind == "parallel":
+            left = {"heads": att_heads, "kv_heads": att_kv_heads, "dim": att_dim, "vdim": att_vdim, "mask": {"size": window, "pool": pool},
+                    "scale": scale, "softcap": softcap}
+            if rot_dims:
+                left["rot"] = {"dims": rot_dims, "base": rot_base}
+            mixer = {"left": left, "right": {"heads": ssd_heads, "vdim": ssd_vdim, "state": state, "groups": groups, "norm_groups": norm_groups, "conv": ssd_taps}}
+        else:
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": taps}
+        out.append({"type": kind, "mixer": mixer, "mlp": None if i in no_ff_layers else {"kind": "dense", "ff": ff}})
+    return {"architecture": "Nelovik", "vocab": vocab, "width": width, "layers": out, "norm": {"eps": eps}}
+
+
+def tensor_shapes(config: dict) -> Dict[str, tuple]:
+    d = config["width"]
+    out = {"embed": (config["vocab"], d)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        out[p + "norm1"] = (d,)
+        if layer["type"] == "parallel":
+            a, s = m["left"], m["right"]
+            q = p + "mix.left."
+            H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            for name, shape in (("q", (H * dk, d)), ("q.b", (H * dk,)), ("k", (G * dk, d)), ("k.b", (G * dk,)), ("v", (G * dv, d)), ("v.b", (G * dv,)),
+                                ("q.norm", (H * dk,)), ("k.norm", (G * dk,)), ("sink", (H,)), ("o", (d, H * dv)), ("out", (d,))):
+                out[q + name] = shape
+            r = p + "mix.right."
+            inner, gn = s["heads"] * s["vdim"], s["groups"] * s["state"]
+            for name, shape in (("in", (2 * inner + 2 * gn + s["heads"], d)), ("conv", (inner + 2 * gn, s["conv"])), ("conv.b", (inner + 2 * gn,)),
+                                ("dt_bias", (s["heads"],)), ("A_log", (s["heads"],)), ("D", (s["heads"],)), ("norm", (inner,)), ("o", (d, inner)), ("out", (d,))):
+                out[r + name] = shape
+        else:
+            H, G, dk, dv, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            for name, shape in (("q", (G * dk, d)), ("q.conv", (G * dk, taps)), ("k", (G * dk, d)), ("k.conv", (G * dk, taps)), ("v", (H * dv, d)),
+                                ("v.conv", (H * dv, taps)), ("b", (H, d)), ("a", (H, d)), ("A_log", (H,)), ("dt_bias", (H,)), ("norm", (dv,)),
+                                ("g", (H * dv, d)), ("o", (d, H * dv))):
+                out[p + "mix." + name] = shape
+        if layer.get("mlp") is not None:
+            out[p + "norm2"] = (d,)
+            out.update({p + "mlp.up": (layer["mlp"]["ff"], d), p + "mlp.down": (d, layer["mlp"]["ff"]), p + "mlp.act": (2,)})
+    out["final.norm"] = (d,)
+    out["head"] = (config["vocab"], d)
+    return out
+
+
+def random_weights(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """bf16 tensors of a scale at which every mechanism matters (decays well inside (0, 1), sinks comparable to the scores)."""
+    g = torch.Generator().manual_seed(seed)
+    W = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.split(".")[-1]
+        if len(shape) == 2 and leaf != "conv":
+            v = torch.randn(shape, generator=g) * (1.0 if name == "embed" else 1.5 / math.sqrt(shape[1]))
+        elif leaf == "conv":
+            v = torch.randn(shape, generator=g) * 0.5
+        elif leaf == "A_log":
+            v = torch.log(0.3 + 2.0 * torch.rand(shape, generator=g))
+        elif leaf == "dt_bias":
+            v = torch.randn(shape, generator=g) * 0.7 - 0.5
+        elif leaf in ("sink", "D"):
+            v = torch.randn(shape, generator=g)
+        elif leaf == "act":
+            v = torch.tensor([0.3, 0.8]) + torch.randn(2, generator=g) * 0.2
+        elif leaf == "b":                               # projection biases
+            v = torch.randn(shape, generator=g) * 0.3
+        else:                                           # norm weights
+            v = 1.0 + torch.randn(shape, generator=g) * 0.2
+        W[name] = v.to(torch.bfloat16)
+    return W
