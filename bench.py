@@ -12,7 +12,7 @@ N > 1 (torchrun, one rank per GPU): independent replicas of the workload, no dat
 collective (weak scaling); "131k" runs the sequence-parallel forward instead.
 Workload "zaverax" (an option; the default workload and its JSON contract are unchanged): the Zaverax design beside StripedHyena at
 equal layer sizes, prefill and decode, with a per-kernel roofline breakdown (bench_arch).  Workload "movalorn": the same for the
-Movalorn design beside Zaverax, the closest family.
+Movalorn design beside Zaverax, the closest family.  Workload "nelovik": the Nelovik design beside Zaverax likewise.
 --impl reference: the reference's own CPU implementation of the path.  stripedhyena==0.2.2 is
 not installable offline, so this arm times the oracle restatement (kind "port") on the host
 cores, rank 0 only, on a bounded sample of the same workload.
@@ -630,6 +630,33 @@ def _movalorn_models(size, dev):
     return mv, zv
 
 
+def _nelovik_models(size, dev):
+    """A Nelovik model and a Zaverax model (the closest family: fp32 stream, matrix-state recurrent layers plus one windowed-attention
+    layer) of equal width, depth, head count, window and feed-forward width, random weights.  Nelovik: three gated-delta layers with
+    heads of 128 x 128 (as many key heads as heads, 4 taps) and one parallel layer -- attention heads of 128 / 128, 64 rotated entries,
+    blocks of 64 tokens pooled before the window, beside a state-space mixer of width-many channels in heads of 64 with state 128."""
+    from evo_b200.nelovik import Nelovik, NelovikConfig
+    from evo_b200.zaverax import Zaverax, ZaveraxConfig
+    s = ARCH_SIZES[size]
+    d, H = s["width"], s["heads"]
+    ff = (8 * d // 3 + 255) // 256 * 256
+    rec = {"type": "hgrn2", "mixer": {"heads": H, "dim": 128, "vdim": 128}, "mlp": {"kind": "dense", "ff": ff}}
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": H, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.5, "mask": {"size": 1024, "keep_first": 0}},
+           "mlp": {"kind": "dense", "ff": ff}}
+    zc = {"architecture": "Zaverax", "vocab": 512, "width": d, "layers": [rec, att, rec, rec], "norm": {"eps": 1e-5}, "canon": {"taps": 3},
+          "loop": {"start": 0, "stop": 0, "times": 1}, "residual_mult": 0.5, "logit_softcap": 15.0}
+    zv = Zaverax(ZaveraxConfig.from_dict(zc)).init_random(0, device=dev)
+    mlp = {"kind": "dense", "ff": ff}
+    delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "conv": 4}, "mlp": mlp}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": 1024, "pool": 64},
+                 "rot": {"dims": 64, "base": 10000.0}},
+        "right": {"heads": d // 64, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}}}
+    nc = {"architecture": "Nelovik", "vocab": 512, "width": d, "norm": {"eps": 1e-5}, "layers": [delta, par, delta, delta]}
+    nv = Nelovik(NelovikConfig.from_dict(nc)).init_random(0, device=dev)
+    return nv, zv
+
+
 def bench_arch(args):
     """--workload zaverax: prefill and decode throughput of the Zaverax design beside StripedHyena at equal layer sizes (random
     weights, 4 layers each, one of them attention), with a per-kernel breakdown against the measured rooflines.  Inputs are larger
@@ -642,16 +669,17 @@ def bench_arch(args):
     warmup = max(3, args.warmup if args.warmup is not None else 3)
     fp32_lane_ops = 148 * 128 * peaks.get("sm_max_mhz", 1965.0) * 1e6        # CUDA-core fp32 instructions (lanes) per second at the maximum clock
     bound = {"gemm": ("flop/s", peaks["bf16_tflops"] * 1e12), "gemm_simt": ("flop/s", 2 * fp32_lane_ops), "attn": ("flop/s", peaks["bf16_tflops"] * 1e12),
-             "window_attn": ("flop/s", peaks["bf16_tflops"] * 1e12), "hgrn2": ("fp32 lane-op/s", fp32_lane_ops)}
+             "window_attn": ("flop/s", peaks["bf16_tflops"] * 1e12), "hgrn2": ("fp32 lane-op/s", fp32_lane_ops),
+             "gated_delta": ("fp32 lane-op/s", fp32_lane_ops), "ssd": ("fp32 lane-op/s", fp32_lane_ops)}
     family = args.workload
-    other = {"zaverax": "stripedhyena", "movalorn": "zaverax"}[family]
+    other = {"zaverax": "stripedhyena", "movalorn": "zaverax", "nelovik": "zaverax"}[family]
     bound.update({"mingru": ("B/s", peaks["hbm_gbs"] * 1e9), "latent_decode": ("B/s", peaks["hbm_gbs"] * 1e9)})
     out = {"workload": family, "metric": f"tokens/sec, prefill and decode, {family} beside {other} at equal sizes", "unit": "tok/s", "dtype": "bf16",
            "data": "synthetic", "steps": steps, "warmup": warmup, "peaks": peaks, "sizes": {}}
     launches = 0
     with ClockSampler(0) as clocks:
         for size, s in ARCH_SIZES.items():
-            zv, sh = _arch_models(size, dev) if family == "zaverax" else _movalorn_models(size, dev)
+            zv, sh = {"zaverax": _arch_models, "movalorn": _movalorn_models, "nelovik": _nelovik_models}[family](size, dev)
             rec = {}
             for name, model in ((family, zv), (other, sh)):
                 B, L = s["prefill"]
@@ -726,14 +754,14 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS) + ["zaverax", "movalorn"])
+    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS) + ["zaverax", "movalorn", "nelovik"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="default workload only: skip the sp131k / gen sub-records")
     ap.add_argument("--no-gen", action="store_true", help="skip the cached-generation sub-record")
     ap.add_argument("--sub-steps", type=int, default=3, help="timed steps of the 131k sub-record")
     ap.add_argument("--gen-tokens", type=int, default=None, help="new tokens of the end-to-end generate() run (default: 4096 = BASELINE configs[3])")
     args = ap.parse_args()
-    if args.workload in ("zaverax", "movalorn"):
+    if args.workload in ("zaverax", "movalorn", "nelovik"):
         return bench_arch(args)
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -236,7 +236,8 @@ SIGNATURES = {
     "evo_conv_act": (C.c_int, [C.POINTER(ConvActParams), C.c_void_p]),
     "evo_xielu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "evo_gated_group_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
-    "evo_gated_delta_fwd": (C.c_int, [C.POINTER(GatedDeltaParams), C.c_void_p]),
+    "evo_gated_delta_workspace": (C.c_size_t, [C.POINTER(GatedDeltaParams)]),
+    "evo_gated_delta_fwd": (C.c_int, [C.POINTER(GatedDeltaParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "evo_ssd_fwd": (C.c_int, [C.POINTER(SsdParams), C.c_void_p]),
     "evo_qk_prep": (C.c_int, [C.POINTER(QkPrepParams), C.c_void_p]),
     "evo_pool_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),

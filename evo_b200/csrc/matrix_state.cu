@@ -4,8 +4,11 @@
 // with everything around them that the recurrence consumes computed here in fp32 from the activated projections: the unit norms of
 // q and k, sigmoid / softplus / exponentials of the per-head gates, and for the delta rule the head's RMS norm, weight and SiLU gate.
 //
-// One CTA per (head, sequence).  Column j of the state belongs to LPC adjacent lanes of one warp, each holding RPT rows
-// (lane l: rows l*RPT .. l*RPT+RPT); column sums (S^T k, S^T q) are folded with shuffles, so the time loop has no barrier.
+// One CTA per (head, sequence, group of value channels).  Column j of the state belongs to LPC adjacent lanes of one warp, each
+// holding RPT rows (lane l: rows l*RPT .. l*RPT+RPT); column sums (S^T k, S^T q) are folded with shuffles, so the time loop has no
+// barrier.  Value channels are independent in both recurrences: a head whose state does not fit one CTA's registers, or a call
+// that would leave SMs idle, is spread over several CTAs by value channel; the delta rule's read-outs then go to an fp32
+// workspace and a second small kernel applies the head norm, weight and gate.
 // TCH tokens are staged per round in shared memory: (k, q) pairs per state row, values, and the per-token numbers.
 // The delta rule needs S^T k before it can write: both products are taken from the decayed state in one pass,
 //   p = (gS)^T k,  r = (gS)^T q,  u = beta (v - p),  o = r + u (k . q),
@@ -14,6 +17,7 @@
 #include "common.cuh"
 #include "../../include/evo_b200.h"
 #include <math.h>
+#include <algorithm>
 
 using namespace evo;
 
@@ -45,13 +49,13 @@ struct ScanArgs {
   float* state; int zero_start;
   // delta epilogue
   const void* gate; int64_t ldg; const void* norm_w; float eps; void* out; int64_t ldo;
-  // ssd output
+  // ssd output, or the delta rule's un-normed read-outs when a head is spread over several CTAs: (rows, H*dv) fp32
   float* y;
   int B; int64_t L; int H, G, dk, dv;
 };
 
 template <typename T, int RPT, int MODE>
-__global__ void __launch_bounds__(RPT <= 32 ? 1024 : 512, 1) matrix_state_kernel(ScanArgs p, int LPC, int dvp) {
+__global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) matrix_state_kernel(ScanArgs p, int LPC, int dvp) {
   extern __shared__ __align__(16) float smem[];
   const int dk = p.dk, dv = p.dv, dkp = LPC * RPT;
   float2* kq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]   (key, query) per state row
@@ -60,7 +64,8 @@ __global__ void __launch_bounds__(RPT <= 32 ? 1024 : 512, 1) matrix_state_kernel
   float* os = sc + TCH * 4;                                // [TCH][dvp]   delta read-outs
   const int h = blockIdx.x, b = blockIdx.y, g = h / (p.H / p.G);
   const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nw = nthr >> 5;
-  const int j = tid / LPC, l = tid % LPC;
+  const int j0 = blockIdx.z * dvp;                         // first value channel of this CTA
+  const int jl = tid / LPC, l = tid % LPC, j = j0 + jl;
   const bool live = j < dv;
   const T* kp = (const T*)p.kk + (int64_t)g * dk;
   const T* qp = (const T*)p.qq + (int64_t)g * dk;
@@ -112,12 +117,12 @@ __global__ void __launch_bounds__(RPT <= 32 ? 1024 : 512, 1) matrix_state_kernel
         }
         if (lane == 0) { sc[tt * 4 + 0] = expf(-A * dt); sc[tt * 4 + 1] = Dh; }
       }
-      for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = c < dv ? ldf(vp + row * p.ld + c) : 0.f;
+      for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = j0 + c < dv ? ldf(vp + row * p.ld + j0 + c) : 0.f;
     }
     __syncthreads();
     // ---- time loop
     for (int tt = 0; tt < nt; ++tt) {
-      const float v = vs[tt * dvp + j];
+      const float v = vs[tt * dvp + jl];
       const float dec = sc[tt * 4 + 0];
       const float4* e = reinterpret_cast<const float4*>(kq + tt * dkp + l * RPT);       // two state rows per 16-byte read
       if (MODE == MODE_DELTA) {
@@ -136,7 +141,11 @@ __global__ void __launch_bounds__(RPT <= 32 ? 1024 : 512, 1) matrix_state_kernel
           S[2 * r] = fmaf(f.x, u, S[2 * r]);
           S[2 * r + 1] = fmaf(f.z, u, S[2 * r + 1]);
         }
-        if (l == 0) os[tt * dvp + j] = fmaf(u, sc[tt * 4 + 2], pq);
+        const float o = fmaf(u, sc[tt * 4 + 2], pq);
+        if (l == 0) {
+          if (p.y) { if (live) p.y[((row0 + tt) * p.H + h) * dv + j] = o; }
+          else os[tt * dvp + jl] = o;
+        }
       } else {
         float y = 0.f;
 #pragma unroll
@@ -149,7 +158,7 @@ __global__ void __launch_bounds__(RPT <= 32 ? 1024 : 512, 1) matrix_state_kernel
         if (l == 0 && live) p.y[((row0 + tt) * p.H + h) * dv + j] = fmaf(sc[tt * 4 + 1], v, y);
       }
     }
-    if (MODE == MODE_DELTA) {
+    if (MODE == MODE_DELTA && !p.y) {
       __syncthreads();
       // head norm, weight, SiLU gate, store: one warp per token
       const bf16* nwt = (const bf16*)p.norm_w;
@@ -179,31 +188,70 @@ __global__ void __launch_bounds__(RPT <= 32 ? 1024 : 512, 1) matrix_state_kernel
   }
 }
 
-struct Plan { int rpt, lpc, dvp; };
-// LPC (a power of two <= 32) lanes per column with RPT rows each; fewest rows per thread that keep the CTA within 1024 threads
-inline Plan plan(int dk, int dv) {
-  const int dvp = (dv + 31) / 32 * 32;      // (dvp * LPC) is then a multiple of 32 and a column never straddles two warps
-  for (int rpt : {4, 8, 16, 32, 64}) {
-    int lpc = 1;
-    while (lpc * rpt < dk) lpc <<= 1;
-    if (lpc <= 32 && (int64_t)lpc * dvp <= (rpt <= 32 ? 1024 : 512)) return {rpt, lpc, dvp};
+// head norm, weight and SiLU gate of the delta rule's read-outs when a head was spread over several CTAs: one warp per (row, head)
+template <typename T>
+__global__ void __launch_bounds__(256) delta_head_norm_kernel(ScanArgs p) {
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (int64_t)p.B * p.L * p.H) return;
+  const int64_t row = wid / p.H; const int h = (int)(wid % p.H);
+  const float* r = p.y + wid * p.dv;
+  float ss = 0.f;
+  for (int c = lane; c < p.dv; c += 32) ss = fmaf(r[c], r[c], ss);
+  ss = warp_sum(ss);
+  const float rstd = 1.0f / sqrtf(ss / (float)p.dv + p.eps);
+  T* orow = (T*)p.out + row * p.ldo;
+  const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * p.dv;
+  const bf16* nw = (const bf16*)p.norm_w;
+  for (int c = lane; c < p.dv; c += 32) {
+    const float gv = ldf(grow + c);
+    stf(orow + h * p.dv + c, r[c] * rstd * __bfloat162float(nw[c]) * (gv / (1.f + expf(-gv))));
   }
-  return {0, 0, 0};
+  if (h == p.H - 1)
+    for (int64_t c = (int64_t)p.H * p.dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+}
+
+struct Plan { int rpt, lpc, dvc, chunks; };
+inline int thread_limit(int rpt) { return rpt <= 8 ? 1024 : (rpt <= 32 ? 512 : 256); }      // registers: rpt state rows per thread
+// about 8 lanes per column (three shuffle steps per fold), RPT = rows / lanes; the value channels a CTA takes follow from its
+// thread limit, and long calls on few (head, sequence) pairs are spread further so that every SM has a CTA
+inline Plan plan(int dk, int dv, int64_t ctas, int64_t L) {
+  const int dvp = (dv + 31) / 32 * 32;
+  int rpt = 4;
+  while (rpt < 64 && rpt * 8 < dk) rpt <<= 1;
+  int lpc = 1;
+  while (lpc * rpt < dk) lpc <<= 1;
+  if (lpc > 32) return {0, 0, 0, 0};
+  const int per_cta = thread_limit(rpt) / lpc / 32 * 32;             // whole warps of columns
+  if (per_cta < 32) return {0, 0, 0, 0};
+  int chunks = (dvp + per_cta - 1) / per_cta;
+  if (L >= 256 && ctas * chunks * 2 <= device_sm_count()) chunks = (int)std::min<int64_t>(dvp / 32, device_sm_count() / ctas);
+  const int dvc = (dvp / 32 + chunks - 1) / chunks * 32;
+  return {rpt, lpc, dvc, (dv + dvc - 1) / dvc};
 }
 
 template <typename T, int RPT, int MODE>
 int launch(const ScanArgs& a, const Plan& pl, cudaStream_t st, const char* what) {
-  const size_t smem = sizeof(float) * ((size_t)2 * TCH * pl.lpc * RPT + (size_t)2 * TCH * pl.dvp + (size_t)TCH * 4);
+  const size_t smem = sizeof(float) * ((size_t)2 * TCH * pl.lpc * RPT + (size_t)2 * TCH * pl.dvc + (size_t)TCH * 4);
   auto kern = matrix_state_kernel<T, RPT, MODE>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(a.H, a.B), dim3(pl.lpc * pl.dvp), smem, st>>>(a, pl.lpc, pl.dvp);
+  kern<<<dim3(a.H, a.B, pl.chunks), dim3(pl.lpc * pl.dvc), smem, st>>>(a, pl.lpc, pl.dvc);
+  int rc = check_launch(what);
+  if (rc || MODE != MODE_DELTA || !a.y) return rc;
+  const int64_t warps = (int64_t)a.B * a.L * a.H;
+  delta_head_norm_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(a);
   return check_launch(what);
 }
 
 template <typename T, int MODE>
-int dispatch(const ScanArgs& a, cudaStream_t st, const char* what) {
-  const Plan pl = plan(a.dk, a.dv);
-  if (pl.rpt == 0) { set_error("%s: a state of %d x %d per head does not fit one CTA (rows <= 2048, value channels <= 512)", what, a.dk, a.dv); return -1; }
+int dispatch(ScanArgs a, void* workspace, size_t workspace_bytes, cudaStream_t st, const char* what) {
+  const Plan pl = plan(a.dk, a.dv, (int64_t)a.B * a.H, a.L);
+  if (pl.rpt == 0) { set_error("%s: a state of %d rows per head does not fit (rows <= 2048)", what, a.dk); return -1; }
+  if (MODE == MODE_DELTA && pl.chunks > 1) {
+    const size_t need = sizeof(float) * (size_t)a.B * a.L * a.H * a.dv;
+    if (!workspace || workspace_bytes < need) { set_error("%s: workspace too small (%zu < %zu)", what, workspace_bytes, need); return -1; }
+    a.y = (float*)workspace;
+  }
   switch (pl.rpt) {
     case 4: return launch<T, 4, MODE>(a, pl, st, what);
     case 8: return launch<T, 8, MODE>(a, pl, st, what);
@@ -215,7 +263,12 @@ int dispatch(const ScanArgs& a, cudaStream_t st, const char* what) {
 
 }  // namespace
 
-extern "C" int evo_gated_delta_fwd(const evo_gated_delta_params* p, void* stream) {
+extern "C" size_t evo_gated_delta_workspace(const evo_gated_delta_params* p) {
+  const Plan pl = plan(p->dk, p->dv, (int64_t)p->B * p->H, p->L);
+  return pl.chunks > 1 ? sizeof(float) * (size_t)p->B * p->L * p->H * p->dv : 0;
+}
+
+extern "C" int evo_gated_delta_fwd(const evo_gated_delta_params* p, void* workspace, size_t workspace_bytes, void* stream) {
   EVO_REQUIRE(p->q && p->k && p->v && p->b && p->a && p->gate && p->A_log && p->dt_bias && p->norm_w && p->out, "evo_gated_delta_fwd: null argument");
   EVO_REQUIRE(p->B >= 0 && p->L >= 0 && p->H > 0 && p->G > 0 && p->H % p->G == 0 && p->dk > 0 && p->dv > 0 && p->ldo >= (int64_t)p->H * p->dv,
               "evo_gated_delta_fwd: bad shape");
@@ -228,7 +281,8 @@ extern "C" int evo_gated_delta_fwd(const evo_gated_delta_params* p, void* stream
   a.state = p->state; a.zero_start = p->zero_start;
   a.gate = p->gate; a.ldg = p->ldz; a.norm_w = p->norm_w; a.eps = p->eps; a.out = p->out; a.ldo = p->ldo;
   a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->G; a.dk = p->dk; a.dv = p->dv;
-  return p->dtype ? dispatch<float, MODE_DELTA>(a, (cudaStream_t)stream, "evo_gated_delta_fwd") : dispatch<bf16, MODE_DELTA>(a, (cudaStream_t)stream, "evo_gated_delta_fwd");
+  return p->dtype ? dispatch<float, MODE_DELTA>(a, workspace, workspace_bytes, (cudaStream_t)stream, "evo_gated_delta_fwd")
+                  : dispatch<bf16, MODE_DELTA>(a, workspace, workspace_bytes, (cudaStream_t)stream, "evo_gated_delta_fwd");
 }
 
 extern "C" int evo_ssd_fwd(const evo_ssd_params* p, void* stream) {
@@ -242,5 +296,5 @@ extern "C" int evo_ssd_fwd(const evo_ssd_params* p, void* stream) {
   a.state = p->state; a.zero_start = p->zero_start;
   a.y = p->y;
   a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->G; a.dk = p->N; a.dv = p->dv;
-  return p->dtype ? dispatch<float, MODE_SSD>(a, (cudaStream_t)stream, "evo_ssd_fwd") : dispatch<bf16, MODE_SSD>(a, (cudaStream_t)stream, "evo_ssd_fwd");
+  return p->dtype ? dispatch<float, MODE_SSD>(a, nullptr, 0, (cudaStream_t)stream, "evo_ssd_fwd") : dispatch<bf16, MODE_SSD>(a, nullptr, 0, (cudaStream_t)stream, "evo_ssd_fwd");
 }

@@ -8,7 +8,9 @@
 // strides are multiples of 8.  A warp keeps both maps' output accumulators (16 x dv fp32 each) in registers and handles one map
 // at a time (scores -> softmax -> P.V), so only one 16 x 64 tile of probabilities is live.
 // Head sizes are padded to 16 in shared memory (zero columns); dk <= 128, dv <= 128 and dv % 8 == 0, otherwise the CUDA-core
-// kernel runs.  The tile walk is the CUDA-core kernel's: [0, keep_first) and the union of the CTA's windows.
+// kernel runs.  The tile walk is the CUDA-core kernel's: [0, keep_first), the pooled blocks that the CTA's last query sees, and the
+// union of the CTA's windows.  A soft cap is applied to the fp32 scores before the softmax (tanh from ex2 and a division), and a
+// sink enters the denominators at the end.
 #include "common.cuh"
 #include "mma_sync.cuh"
 #include "../../include/evo_b200.h"
@@ -80,10 +82,24 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
     for (int n = 0; n < NV8; ++n) O[m][n][0] = O[m][n][1] = O[m][n][2] = O[m][n][3] = 0.f;
   }
   const bf16* Qw = Qs + (w * QROWS) * qst;
-  const float scale2 = p.scale * 1.4426950408889634f;
+  const float LOG2E = 1.4426950408889634f;
+  const float scale2 = p.scale * LOG2E;
+  // soft cap: cap * tanh(s / cap) with tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1), in base-2 units like the plain scores
+  const bool capped = p.softcap > 0.f;
+  const float cap_in = capped ? p.scale / p.softcap * 2.f * LOG2E : 0.f, cap_out = p.softcap * LOG2E;
+  // pooled blocks before the window: block b is seen from position i iff b < (i - window + 1) / pool
+  const auto seen = [&](int64_t i) -> int64_t { const int64_t n = i - p.window + 1; return (p.pool > 0 && n > 0) ? n / p.pool : 0; };
+  const int64_t pool_hi = windowed ? seen(i_hi) : 0;
+  const int64_t seen0 = windowed ? seen(i0) : 0, seen1 = windowed ? seen(i1) : 0, wseen_lo = windowed ? seen(wi_lo) : 0, wseen_hi = windowed ? seen(wi_hi) : 0;
+  const bf16* pkb = pool_hi ? (const bf16*)p.pool_k + (int64_t)b * p.pool_batch_stride + (int64_t)g * NM * dk : nullptr;
+  const bf16* pvb = pool_hi ? (const bf16*)p.pool_v + (int64_t)b * p.pool_batch_stride + (int64_t)g * dv : nullptr;
 
-  for (int part = 0; part < 2; ++part) {
-    const int64_t lo = part == 0 ? 0 : win_lo, hi = part == 0 ? keep_hi : i_hi + 1;
+  for (int part = 0; part < 3; ++part) {               // kept first tokens, pooled blocks, window
+    const int64_t lo = part == 2 ? win_lo : 0, hi = part == 0 ? keep_hi : (part == 1 ? pool_hi : i_hi + 1);
+    const bool pooled = part == 1;
+    const bf16* kbase = pooled ? pkb : kb;
+    const bf16* vbase = pooled ? pvb : vb;
+    const int64_t kstr = pooled ? p.pool_tok_stride : p.k_tok_stride, vstr = pooled ? p.pool_tok_stride : p.v_tok_stride;
     for (int64_t k0 = lo; k0 < hi; k0 += KT) {
       const int nk = (int)min((int64_t)KT, hi - k0);
       __syncthreads();
@@ -91,7 +107,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
         for (int r = vr0, cc = vc0; r < KT; ) {
           const int m = cc >= cpm, e = (cc - m * cpm) * 8;
           uint4 v = zero4;
-          if (r < nk && e < dk) v = *reinterpret_cast<const uint4*>(kb + (k0 + r) * p.k_tok_stride + m * dk + e);
+          if (r < nk && e < dk) v = *reinterpret_cast<const uint4*>(kbase + (k0 + r) * kstr + m * dk + e);
           *reinterpret_cast<uint4*>(Ks + r * kst + cc * 8) = v;
           r += vstep.x; cc += vstep.y;
           if (cc >= c8n) { cc -= c8n; ++r; }
@@ -99,29 +115,35 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
         for (int idx = tid; idx < KT * NV8; idx += WARPS * 32) {
           const int r = idx / NV8, c = (idx % NV8) * 8;
           uint4 v = zero4;
-          if (r < nk && c < dv) v = *reinterpret_cast<const uint4*>(vb + (k0 + r) * p.v_tok_stride + c);
+          if (r < nk && c < dv) v = *reinterpret_cast<const uint4*>(vbase + (k0 + r) * vstr + c);
           *reinterpret_cast<uint4*>(Vs + r * vst + c) = v;
         }
       } else {
         for (int idx = tid; idx < KT * NM * dkp; idx += WARPS * 32) {
           const int r = idx / (NM * dkp), c = idx % (NM * dkp), m = c / dkp, e = c % dkp;
           bf16 v = __float2bfloat16_rn(0.f);
-          if (r < nk && e < dk) v = kb[(k0 + r) * p.k_tok_stride + m * dk + e];
+          if (r < nk && e < dk) v = kbase[(k0 + r) * kstr + m * dk + e];
           Ks[r * kst + c] = v;
         }
         for (int idx = tid; idx < KT * NV8 * 8; idx += WARPS * 32) {
           const int r = idx / (NV8 * 8), c = idx % (NV8 * 8);
           bf16 v = __float2bfloat16_rn(0.f);
-          if (r < nk && c < dv) v = vb[(k0 + r) * p.v_tok_stride + c];
+          if (r < nk && c < dv) v = vbase[(k0 + r) * vstr + c];
           Vs[r * vst + c] = v;
         }
       }
       __syncthreads();
       // a tile none of the warp's rows can see
       const int64_t t_lo = k0, t_hi = k0 + nk - 1;
-      if (t_lo > wi_hi) continue;
-      if (windowed && wi_lo - t_hi >= p.window && t_lo >= p.keep_first) continue;
-      const bool full = nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
+      bool full;
+      if (pooled) {
+        if (t_lo >= wseen_hi) continue;
+        full = nk == KT && t_hi < wseen_lo;
+      } else {
+        if (t_lo > wi_hi) continue;
+        if (windowed && wi_lo - t_hi >= p.window && t_lo >= p.keep_first) continue;
+        full = nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
+      }
 
 #pragma unroll
       for (int m = 0; m < NM; ++m) {
@@ -151,7 +173,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
           for (int n = 0; n < KT / 8; ++n) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              const float s = Pm[0][n][c] * scale2;
+              const float s = capped ? cap_out * (1.f - __fdividef(2.f, ex2(Pm[0][n][c] * cap_in) + 1.f)) : Pm[0][n][c] * scale2;
               Pm[0][n][c] = s;
               if (c < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
             }
@@ -163,8 +185,10 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
           for (int c = 0; c < 4; ++c) {
             const int64_t kj = k0 + n * 8 + qc + (c & 1);
             const int64_t i = (c < 2) ? i0 : i1;
-            const bool vis = (n * 8 + qc + (c & 1)) < nk && kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first);
-            const float s = vis ? Pm[0][n][c] * scale2 : -INFINITY;        // base-2 exponent: exp(x) = 2^(x log2 e)
+            const bool vis = (n * 8 + qc + (c & 1)) < nk &&
+                             (pooled ? kj < ((c < 2) ? seen0 : seen1) : (kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first)));
+            const float sc = capped ? cap_out * (1.f - __fdividef(2.f, ex2(Pm[0][n][c] * cap_in) + 1.f)) : Pm[0][n][c] * scale2;
+            const float s = vis ? sc : -INFINITY;                          // base-2 exponent: exp(x) = 2^(x log2 e)
             Pm[0][n][c] = s;
             if (c < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
           }
@@ -209,7 +233,18 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   }
   // o = a1 / l1 - lambda * a2 / l2, head norm, gate, store
   const int64_t rel_a = rel0 + w * QROWS + qr, rel_b = rel_a + 8;
-  const float il[2][2] = {{1.f / lrun[0][0], 1.f / lrun[0][1]}, {1.f / lrun[NM - 1][0], 1.f / lrun[NM - 1][1]}};
+  float il[2][2] = {{1.f / lrun[0][0], 1.f / lrun[0][1]}, {1.f / lrun[NM - 1][0], 1.f / lrun[NM - 1][1]}};
+  if (p.sink) {      // exp(sink_h) joins the denominator: with mx = max(m, sink), acc / l becomes acc 2^(m-mx) / (l 2^(m-mx) + 2^(sink-mx))
+    const float sk = __bfloat162float(((const bf16*)p.sink)[h]) * LOG2E;
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int m = a == 0 ? 0 : NM - 1;
+        const float mx = fmaxf(mrun[m][r], sk), num = ex2(mrun[m][r] - mx);
+        il[a][r] = num / fmaf(lrun[m][r], num, ex2(sk - mx));
+      }
+  }
   float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll
   for (int n = 0; n < NV8; ++n) {
@@ -262,7 +297,8 @@ int launch(const evo_window_attn_params* p, cudaStream_t st) {
   const size_t smem = sizeof(bf16) * ((size_t)WARPS * QROWS * qst + (size_t)KT * kst + (size_t)KT * vst);
   auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
   const int vec = p->dk % 8 == 0 && p->dv % 8 == 0 && p->q_tok_stride % 8 == 0 && p->k_tok_stride % 8 == 0 && p->v_tok_stride % 8 == 0 &&
-                  p->k_batch_stride % 8 == 0 && p->v_batch_stride % 8 == 0 && a16(p->q) && a16(p->k) && a16(p->v);
+                  p->k_batch_stride % 8 == 0 && p->v_batch_stride % 8 == 0 && a16(p->q) && a16(p->k) && a16(p->v) &&
+                  (p->pool <= 0 || (p->pool_tok_stride % 8 == 0 && p->pool_batch_stride % 8 == 0 && a16(p->pool_k) && a16(p->pool_v)));
   auto kern = window_attn_mma_kernel<NV8, NM>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int c8n = NM * dkp / 8;
@@ -290,6 +326,5 @@ int dispatch(const evo_window_attn_params* p, cudaStream_t st) {
 
 int evo::window_attn_mma(const evo_window_attn_params* p, cudaStream_t st) {
   if (p->dtype != 0 || p->dk * p->n_maps > 256 || p->dk > 128 || p->dv > 128 || p->dv % 8 != 0 || p->Lq < 16) return 1;
-  if (p->pool > 0 || p->sink || p->softcap > 0.f) return 1;      // pooled blocks, sink and soft cap: the CUDA-core kernels
   return p->n_maps == 2 ? dispatch<2>(p, st) : dispatch<1>(p, st);
 }

@@ -160,7 +160,9 @@ class Nelovik(StreamDecoder):
                               A_log=w[p + "A_log"].data_ptr(), dt_bias=w[p + "dt_bias"].data_ptr(), norm_w=w[p + "norm"].data_ptr(),
                               eps=self.config.eps, unit_eps=1e-6, q_scale=m.dim ** -0.5, state=state.data_ptr(), zero_start=zero,
                               out=out.data_ptr(), ldo=ldo, dtype=self._dt, B=B, L=L, H=m.heads, G=m.kv_heads, dk=m.dim, dv=m.vdim)
-        self._record("gated_delta", 4.0 * M * m.heads * m.dim * m.vdim, lambda: check(_lib.lib().evo_gated_delta_fwd(C.byref(gp), self._stream()), "evo_gated_delta_fwd"))
+        nws = _lib.lib().evo_gated_delta_workspace(C.byref(gp))
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev) if nws else None
+        self._record("gated_delta", 4.0 * M * m.heads * m.dim * m.vdim, lambda: check(_lib.lib().evo_gated_delta_fwd(C.byref(gp), ptr(ws), nws, self._stream()), "evo_gated_delta_fwd"))
         return [(self._linear(out, pk["out"], M), pk["out"].Np, None, 1.0)]
 
     def _ssd(self, r, i, s, z, col0, ldz, B, L, rec, fresh):

@@ -530,7 +530,9 @@ typedef struct {
   void* out; int64_t ldo; int dtype;
   int B; int64_t L; int H, G, dk, dv;
 } evo_gated_delta_params;
-int evo_gated_delta_fwd(const evo_gated_delta_params* p, void* stream);
+/* workspace: evo_gated_delta_workspace() bytes (0 unless a head's value channels are spread over several CTAs; the head norm then runs in a second kernel) */
+size_t evo_gated_delta_workspace(const evo_gated_delta_params* p);
+int evo_gated_delta_fwd(const evo_gated_delta_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 /* State-space duality recurrence, per head h (group h / (H/G)), over the activated x (H*dv), Bm, Cm (G*N) of a row and the raw step dt (H):
  *   d = softplus(dt_h + dt_bias_h),  S <- exp(-exp(A_log_h) d) S + d Bm x^T,  y = S^T Cm + D_h x     (S is N x dv, fp32).

@@ -240,6 +240,67 @@ def test_pooled_window_attention_mixer_matches_the_oracle(sizes):
     assert rel(whole16[0], want) < 3e-2 and rel(_portions(bf, tokens, [30] + [1] * 40), want) < 3e-2
 
 
+@pytest.mark.parametrize("H,G,dk,dv,window,pool,cap,L", [(4, 2, 64, 64, 70, 8, 20.0, 300), (2, 2, 128, 128, 130, 64, 0.0, 400), (3, 1, 32, 24, 16, 1, 5.0, 150),
+                                                        (2, 1, 16, 8, 200, 3, 50.0, 330)])
+def test_attention_kernels_agree_on_tokens_blocks_sink_and_cap(H, G, dk, dv, window, pool, cap, L):
+    """The three kernels behind evo_window_attn_fwd on the same bf16 cache: the tensor-core kernel (all rows in one call), the
+    many-query CUDA-core kernel (fp32 copies of the same numbers) and the few-query kernel (one row per call), against a plain
+    softmax over the visible tokens and pooled rows with the sink in the denominator."""
+    from evo_b200._lib import WindowAttnParams
+    g = torch.Generator().manual_seed(L)
+    scale = 2.5 / math.sqrt(dk)                            # scores of a few units either way, so that the cap bends them
+    q = _bf(torch.randn(L, H * dk, generator=g))
+    kv = _bf(torch.randn(L + 5, G * (dk + dv), generator=g))
+    sink = _bf(torch.randn(H, generator=g) * 2)
+    lib = _lib.lib()
+    ldo = (H * dv + 63) // 64 * 64
+    nb = L // pool + 1
+
+    def run(dtype, rows_per_call):
+        dt = 1 if dtype == F32 else 0
+        qd, kvd, sd = q.to(DEV, dtype), kv.to(DEV, dtype).contiguous(), sink.to(DEV)
+        pooled = torch.full((nb, G * (dk + dv)), float("nan"), dtype=dtype, device=DEV)
+        row = G * (dk + dv)
+        check(lib.evo_pool_rows(ptr(kvd), row, kvd.numel(), ptr(pooled), row, pooled.numel(), 1, L, row, pool, 0, None, dt, _stream()))
+        out = torch.empty(L, ldo, dtype=dtype, device=DEV)
+        esz = qd.element_size()
+        for r0 in range(0, L, rows_per_call):
+            n = min(rows_per_call, L - r0)
+            ap = WindowAttnParams(q=qd.data_ptr() + r0 * H * dk * esz, q_tok_stride=H * dk, k=kvd.data_ptr(), v=kvd.data_ptr() + G * dk * esz, k_tok_stride=row, v_tok_stride=row,
+                                  k_batch_stride=kvd.numel(), v_batch_stride=kvd.numel(), out=out.data_ptr() + r0 * ldo * esz, ldo=ldo, dtype=dt, B=1, Lq=n, H=H, G=G,
+                                  dk=dk, dv=dv, n_maps=1, q_pos0=r0, window=window, scale=scale, softcap=cap, sink=sd.data_ptr(), pool=pool,
+                                  pool_k=pooled.data_ptr(), pool_v=pooled.data_ptr() + G * dk * esz, pool_tok_stride=row, pool_batch_stride=pooled.numel())
+            check(lib.evo_window_attn_fwd(C.byref(ap), _stream()))
+        return out[:, :H * dv].double().cpu(), pooled
+
+    qf, kf = q.double().view(L, H, dk), kv.double()
+    want = torch.zeros(L, H, dv, dtype=torch.float64)
+    pk = torch.stack([kf[b * pool:(b + 1) * pool].mean(0) for b in range(L // pool)]) if L >= pool else kf[:0]
+    for h in range(H):
+        gi = h // (H // G)
+        for i in range(L):
+            js, bs = O.visible_tokens(i, window), O.visible_blocks(i, window, pool)
+            rows = torch.cat([kf[js], pk[bs]]) if bs else kf[js]
+            sc = rows[:, gi * dk:(gi + 1) * dk] @ qf[i, h] * scale
+            if cap > 0:
+                sc = cap * torch.tanh(sc / cap)
+            mx = torch.maximum(sc.max(), sink[h].double())
+            e = torch.exp(sc - mx)
+            want[i, h] = (e[:, None] * rows[:, G * dk + gi * dv:G * dk + (gi + 1) * dv]).sum(0) / (e.sum() + torch.exp(sink[h].double() - mx))
+    want = want.view(L, H * dv)
+    many32, pooled32 = run(F32, L)
+    _close(pooled32[:L // pool, :], pk, 1e-6, "pooled rows")
+    _close(many32, want, 2e-5, "many-query kernel, fp32")
+    _close(run(F32, 1)[0], want, 2e-5, "few-query kernel, fp32")
+    _close(run(F32, 3)[0], want, 2e-5, "few-query kernel, three rows a call")
+    # bf16: pooled rows are rounded when stored, outputs when written
+    tensor, _ = run(B16, L)
+    few, _ = run(B16, 2)
+    _close(tensor, want, 1.5e-2, "tensor-core kernel")
+    _close(few, want, 1.5e-2, "few-query kernel, bf16")
+    _close(tensor, few, 1e-2, "tensor-core kernel against the few-query kernel")
+
+
 # ------------------------------------------------------------------ edges of the window and of the pooled blocks
 def _dominant_token(cfg, W, plain, odd, gain):
     """Weights under which the key of token `odd` beats the key of token `plain` by `gain` in every head, for a query of `plain`, at
