@@ -7,6 +7,8 @@
 #include "common.cuh"
 #include "../../include/evo_b200.h"
 #include <math.h>
+#include <algorithm>
+#include <stdint.h>
 
 using namespace evo;
 
@@ -20,6 +22,25 @@ template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p =
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+// four consecutive elements (16 bytes of fp32, 8 of bf16) as floats, and back
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float* o) { const float4 u = *reinterpret_cast<const float4*>(p); o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w; }
+  static __device__ __forceinline__ void store(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float* o) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    o[0] = __uint_as_float(u.x << 16); o[1] = __uint_as_float(u.x & 0xffff0000u); o[2] = __uint_as_float(u.y << 16); o[3] = __uint_as_float(u.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float* v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 u; u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+template <typename T> inline bool aligned4(const void* p) { return ((uintptr_t)p & (4 * sizeof(T) - 1)) == 0; }
 
 // sum over the CTA (blockDim.x a multiple of 32, at most 1024); every thread gets the result; red: 33 floats
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -40,7 +61,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // ---- evo_sum_norm: one CTA per row; the new row of x is kept in shared memory between the passes
-template <typename T>
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) sum_norm_kernel(evo_sum_norm_params p) {
   extern __shared__ float xs[];          // [D] + 33
   float* red = xs + p.D;
@@ -54,12 +75,41 @@ __global__ void __launch_bounds__(256) sum_norm_kernel(evo_sum_norm_params p) {
     if (b < p.n_branches && p.norm_w[b]) {
       const T* y = (const T*)p.y[b] + src * p.ldy[b];
       float ss = 0.f;
-      for (int c = tid; c < D; c += nt) { const float v = ldf(y + c); ss = fmaf(v, v, ss); }
+      if (VEC) {
+        for (int c = tid * 4; c < D; c += nt * 4) { float v[4]; Vec4<T>::load(y + c, v); ss = fmaf(v[0], v[0], fmaf(v[1], v[1], fmaf(v[2], v[2], fmaf(v[3], v[3], ss)))); }
+      } else {
+        for (int c = tid; c < D; c += nt) { const float v = ldf(y + c); ss = fmaf(v, v, ss); }
+      }
       rstd[b] = 1.0f / sqrtf(block_sum(ss, red) / (float)D + p.eps);
     }
   }
   float* xr = p.x + src * D;
   float ss = 0.f;
+  if (VEC) {
+    for (int c = tid * 4; c < D; c += nt * 4) {
+      float v[4], add[4] = {0.f, 0.f, 0.f, 0.f};
+      Vec4<float>::load(xr + c, v);
+#pragma unroll
+      for (int b = 0; b < EVO_SUM_NORM_BRANCHES; ++b) {
+        if (b < p.n_branches) {
+          float y[4];
+          Vec4<T>::load((const T*)p.y[b] + src * p.ldy[b] + c, y);
+          if (p.norm_w[b]) {
+            float w[4];
+            Vec4<bf16>::load((const bf16*)p.norm_w[b] + c, w);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) y[u] = y[u] * rstd[b] * w[u];
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) add[u] = fmaf(p.scale[b], y[u], add[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { v[u] += add[u]; ss = fmaf(v[u], v[u], ss); }
+      Vec4<float>::store(xs + c, v);
+      if (p.n_branches > 0 && !p.gather) Vec4<float>::store(xr + c, v);
+    }
+  } else
   for (int c = tid; c < D; c += nt) {
     float v = xr[c];
     float add = 0.f;
@@ -83,12 +133,73 @@ __global__ void __launch_bounds__(256) sum_norm_kernel(evo_sum_norm_params p) {
     if (!p.out[n]) continue;
     T* o = (T*)p.out[n] + r * p.ldo;
     const bf16* w = (const bf16*)p.w[n];
+    if (VEC) {
+      for (int c = tid * 4; c < p.ldo; c += nt * 4) {
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (c < D) {                     // D % 4 == 0: a group of four lies inside the row or in the padding
+          float wv[4];
+          Vec4<bf16>::load(w + c, wv);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) v[u] = xs[c + u] * rs * wv[u];
+        }
+        Vec4<T>::store(o + c, v);
+      }
+    } else
     for (int c = tid; c < p.ldo; c += nt) stf(o + c, c < D ? xs[c] * rs * __bfloat162float(w[c]) : 0.f);
   }
 }
 
 // ---- evo_conv_act: a thread owns one channel of one sequence over RT consecutive rows, its last taps inputs in registers
-constexpr int CONV_RT = 16, CONV_MAX_TAPS = 8;
+constexpr int CONV_RT = 32, CONV_MAX_TAPS = 8;
+
+// four channels per thread (8- or 16-byte accesses), taps known at compile time
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128) conv_act4_kernel(evo_conv_act_params p, int write_carry) {
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= p.C) return;
+  constexpr int HALO = TAPS - 1;
+  const int b = blockIdx.z;
+  const int64_t t0 = (int64_t)blockIdx.y * CONV_RT, t1 = min(p.L, t0 + CONV_RT);
+  const T* in = (const T*)p.in + (int64_t)b * p.L * p.ld + c;
+  float* carry = p.carry ? p.carry + (int64_t)b * HALO * p.C + c : nullptr;
+  float w[4][TAPS], win[HALO > 0 ? HALO : 1][4], bias[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) w[u][j] = __bfloat162float(((const bf16*)p.weight)[(int64_t)(c + u) * TAPS + j]);
+  if (p.bias) Vec4<bf16>::load((const bf16*)p.bias + c, bias);
+#pragma unroll
+  for (int j = 0; j < HALO; ++j) {
+    const int64_t s = t0 - HALO + j;
+    win[j][0] = win[j][1] = win[j][2] = win[j][3] = 0.f;
+    if (s >= 0) Vec4<T>::load(in + s * p.ld, win[j]);
+    else if (carry && !p.zero_start) Vec4<float>::load(carry + (int64_t)(HALO + s) * p.C, win[j]);
+  }
+  for (int64_t t = t0; t < t1; ++t) {
+    float cur[4], acc[4];
+    Vec4<T>::load(in + t * p.ld, cur);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float a = fmaf(w[u][HALO], cur[u], bias[u]);
+#pragma unroll
+      for (int j = 0; j < HALO; ++j) a = fmaf(w[u][j], win[j][u], a);
+      acc[u] = p.act == 1 ? silu_f(a) : a;
+    }
+    Vec4<T>::store((T*)p.out + ((int64_t)b * p.L + t) * p.ldo + c, acc);
+#pragma unroll
+    for (int j = 0; j + 1 < HALO; ++j)
+#pragma unroll
+      for (int u = 0; u < 4; ++u) win[j][u] = win[j + 1][u];
+    if (HALO > 0) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) win[HALO - 1][u] = cur[u];
+    }
+  }
+  if (write_carry && carry && t1 == p.L) {
+#pragma unroll
+    for (int j = 0; j < HALO; ++j) Vec4<float>::store(carry + (int64_t)j * p.C, win[j]);
+  }
+}
 
 template <typename T>
 __global__ void __launch_bounds__(128) conv_act_kernel(evo_conv_act_params p, int write_carry) {
@@ -180,6 +291,27 @@ __global__ void __launch_bounds__(256) xielu_kernel(const T* __restrict__ z, int
   }
 }
 
+// four columns per thread, rows along grid.y: no division per element
+template <typename T>
+__global__ void __launch_bounds__(256) xielu4_kernel(const T* __restrict__ z, int64_t ldz, const bf16* __restrict__ coef, T* __restrict__ out, int64_t ldo,
+                                                     int64_t rows, int F) {
+  const float pa = __bfloat162float(coef[0]), qa = __bfloat162float(coef[1]);
+  const float ap = fmaxf(pa, 0.f) + log1pf(expf(-fabsf(pa)));
+  const float an = 0.5f + fmaxf(qa, 0.f) + log1pf(expf(-fabsf(qa)));
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c >= ldo) return;
+  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+    float v[4] = {0.f, 0.f, 0.f, 0.f}, o[4];
+    if (c < F) Vec4<T>::load(z + r * ldz + c, v);           // ldz >= F rounded up to four: the group may read pad columns of z, masked below
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float x = v[u];
+      o[u] = c + u < F ? (x > 0.f ? fmaf(ap * x, x, 0.5f * x) : fmaf(an, expm1f(x) - x, 0.5f * x)) : 0.f;
+    }
+    Vec4<T>::store(out + r * ldo + c, o);
+  }
+}
+
 // ---- evo_gated_group_norm: one warp per (row, part)
 template <typename T>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int64_t ldg, const bf16* __restrict__ nw,
@@ -212,7 +344,15 @@ extern "C" int evo_sum_norm(const evo_sum_norm_params* p, void* stream) {
   const size_t smem = sizeof(float) * ((size_t)p->D + 33);
   EVO_REQUIRE(smem <= 200 * 1024, "evo_sum_norm: width %d too large for one CTA's shared memory", p->D);
   cudaStream_t st = (cudaStream_t)stream;
-  auto kern = p->dtype ? sum_norm_kernel<float> : sum_norm_kernel<bf16>;
+  // four elements per access when every row of every operand starts on a multiple of four elements
+  bool vec = p->D % 4 == 0 && p->ldo % 4 == 0 && ((uintptr_t)p->x & 15) == 0;
+  for (int b = 0; b < p->n_branches; ++b) {
+    vec = vec && p->ldy[b] % 4 == 0 && (p->dtype ? aligned4<float>(p->y[b]) : aligned4<bf16>(p->y[b]));
+    if (p->norm_w[b]) vec = vec && aligned4<bf16>(p->norm_w[b]);
+  }
+  for (int n = 0; n < 2; ++n)
+    if (p->out[n]) vec = vec && aligned4<bf16>(p->w[n]) && (p->dtype ? aligned4<float>(p->out[n]) : aligned4<bf16>(p->out[n]));
+  auto kern = p->dtype ? (vec ? sum_norm_kernel<float, true> : sum_norm_kernel<float, false>) : (vec ? sum_norm_kernel<bf16, true> : sum_norm_kernel<bf16, false>);
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<(unsigned)p->rows, 256, smem, st>>>(*p);
   return check_launch("evo_sum_norm");
@@ -227,7 +367,21 @@ extern "C" int evo_conv_act(const evo_conv_act_params* p, void* stream) {
   const dim3 grid((p->C + 127) / 128, chunks, p->B);
   // with one thread per (sequence, channel) that thread reads the carried inputs before it replaces them; otherwise a second launch does
   const int own = chunks == 1;
-  if (p->dtype) conv_act_kernel<float><<<grid, 128, 0, st>>>(*p, own); else conv_act_kernel<bf16><<<grid, 128, 0, st>>>(*p, own);
+  const bool vec = p->C % 4 == 0 && p->ld % 4 == 0 && p->ldo % 4 == 0 && p->taps <= 4 && (!p->carry || ((uintptr_t)p->carry & 15) == 0) &&
+                   (!p->bias || aligned4<bf16>(p->bias)) &&
+                   (p->dtype ? aligned4<float>(p->in) && aligned4<float>(p->out) : aligned4<bf16>(p->in) && aligned4<bf16>(p->out));
+  if (vec) {
+    const dim3 g4((p->C / 4 + 127) / 128, chunks, p->B);
+#define EVO_CONV4(TT) \
+    switch (p->taps) { \
+      case 1: conv_act4_kernel<TT, 1><<<g4, 128, 0, st>>>(*p, own); break; \
+      case 2: conv_act4_kernel<TT, 2><<<g4, 128, 0, st>>>(*p, own); break; \
+      case 3: conv_act4_kernel<TT, 3><<<g4, 128, 0, st>>>(*p, own); break; \
+      default: conv_act4_kernel<TT, 4><<<g4, 128, 0, st>>>(*p, own); break; \
+    }
+    if (p->dtype) { EVO_CONV4(float) } else { EVO_CONV4(bf16) }
+#undef EVO_CONV4
+  } else if (p->dtype) conv_act_kernel<float><<<grid, 128, 0, st>>>(*p, own); else conv_act_kernel<bf16><<<grid, 128, 0, st>>>(*p, own);
   int rc = check_launch("evo_conv_act");
   if (rc || own || !p->carry || p->taps == 1) return rc;
   const dim3 g2((p->C + 127) / 128, 1, p->B);
@@ -241,6 +395,12 @@ extern "C" int evo_xielu(const void* z, int64_t ldz, const void* coef, void* out
   const int64_t total = rows * ldo;
   const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)device_sm_count() * 16);
   cudaStream_t st = (cudaStream_t)stream;
+  if (ldz % 4 == 0 && ldo % 4 == 0 && ldz >= (F + 3) / 4 * 4 && (dtype ? aligned4<float>(z) && aligned4<float>(out) : aligned4<bf16>(z) && aligned4<bf16>(out))) {
+    const dim3 g4((unsigned)((ldo / 4 + 255) / 256), (unsigned)std::min<int64_t>(rows, 32768));
+    if (dtype) xielu4_kernel<float><<<g4, 256, 0, st>>>((const float*)z, ldz, (const bf16*)coef, (float*)out, ldo, rows, F);
+    else xielu4_kernel<bf16><<<g4, 256, 0, st>>>((const bf16*)z, ldz, (const bf16*)coef, (bf16*)out, ldo, rows, F);
+    return check_launch("evo_xielu");
+  }
   if (dtype) xielu_kernel<float><<<grid, 256, 0, st>>>((const float*)z, ldz, (const bf16*)coef, (float*)out, ldo, rows, F);
   else xielu_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)z, ldz, (const bf16*)coef, (bf16*)out, ldo, rows, F);
   return check_launch("evo_xielu");

@@ -5,7 +5,8 @@
 // q and k, sigmoid / softplus / exponentials of the per-head gates, and for the delta rule the head's RMS norm, weight and SiLU gate.
 //
 // One CTA per (head, sequence, group of value channels).  Column j of the state belongs to LPC adjacent lanes of one warp, each
-// holding RPT rows (lane l: rows l*RPT .. l*RPT+RPT); column sums (S^T k, S^T q) are folded with shuffles, so the time loop has no
+// holding RPT rows in pairs (lane l, pair r: rows 2*(r*LPC + l) and + 1, so that the lanes of a column read consecutive 16-byte
+// (key, query, key, query) entries of shared memory, without bank conflicts); column sums (S^T k, S^T q) are folded with shuffles, so the time loop has no
 // barrier.  Value channels are independent in both recurrences: a head whose state does not fit one CTA's registers, or a call
 // that would leave SMs idle, is spread over several CTAs by value channel; the delta rule's read-outs then go to an fp32
 // workspace and a second small kernel applies the head norm, weight and gate.
@@ -78,7 +79,7 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
   float S[RPT];
 #pragma unroll
   for (int r = 0; r < RPT; ++r) {
-    const int k = l * RPT + r;
+    const int k = 2 * ((r >> 1) * LPC + l) + (r & 1);
     S[r] = (Sg && !p.zero_start && live && k < dk) ? Sg[(int64_t)k * dv + j] : 0.f;
   }
 
@@ -124,12 +125,12 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
     for (int tt = 0; tt < nt; ++tt) {
       const float v = vs[tt * dvp + jl];
       const float dec = sc[tt * 4 + 0];
-      const float4* e = reinterpret_cast<const float4*>(kq + tt * dkp + l * RPT);       // two state rows per 16-byte read
+      const float4* e = reinterpret_cast<const float4*>(kq + tt * dkp) + l;             // two state rows per 16-byte read; pair r at e[r * LPC]
       if (MODE == MODE_DELTA) {
         float pk = 0.f, pq = 0.f;
 #pragma unroll
         for (int r = 0; r < RPT / 2; ++r) {
-          const float4 f = e[r];
+          const float4 f = e[r * LPC];
           S[2 * r] *= dec;          pk = fmaf(S[2 * r], f.x, pk);     pq = fmaf(S[2 * r], f.y, pq);
           S[2 * r + 1] *= dec;      pk = fmaf(S[2 * r + 1], f.z, pk); pq = fmaf(S[2 * r + 1], f.w, pq);
         }
@@ -137,7 +138,7 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
         const float u = sc[tt * 4 + 1] * (v - pk);
 #pragma unroll
         for (int r = 0; r < RPT / 2; ++r) {
-          const float4 f = e[r];
+          const float4 f = e[r * LPC];
           S[2 * r] = fmaf(f.x, u, S[2 * r]);
           S[2 * r + 1] = fmaf(f.z, u, S[2 * r + 1]);
         }
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
         float y = 0.f;
 #pragma unroll
         for (int r = 0; r < RPT / 2; ++r) {
-          const float4 f = e[r];
+          const float4 f = e[r * LPC];
           S[2 * r] = fmaf(dec, S[2 * r], f.x * v);          y = fmaf(S[2 * r], f.y, y);
           S[2 * r + 1] = fmaf(dec, S[2 * r + 1], f.z * v);  y = fmaf(S[2 * r + 1], f.w, y);
         }
@@ -182,7 +183,7 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
   if (Sg && live) {
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-      const int k = l * RPT + r;
+      const int k = 2 * ((r >> 1) * LPC + l) + (r & 1);
       if (k < dk) Sg[(int64_t)k * dv + j] = S[r];
     }
   }

@@ -106,7 +106,7 @@ def test_sum_norm_branches_norms_and_gathered_rows(D, ldo, dtype):
     _close(xd3, x.double() + 0.5 * O.rms(ys[0][:, :D].double(), eps) * nws[0].double(), 1e-6, "sum only")
 
 
-@pytest.mark.parametrize("taps,Cn,L", [(4, 70, 50), (2, 5, 33), (1, 40, 12), (3, 300, 17), (8, 33, 40)])
+@pytest.mark.parametrize("taps,Cn,L", [(4, 72, 90), (2, 5, 33), (1, 40, 12), (3, 300, 17), (8, 33, 70), (4, 70, 50)])
 @pytest.mark.parametrize("dtype", [F32, B16])
 def test_short_convolution_whole_portions_and_steps(taps, Cn, L, dtype):
     B, ld, col0 = 2, Cn + 24, 8
