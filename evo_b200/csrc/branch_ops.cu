@@ -306,7 +306,9 @@ __global__ void __launch_bounds__(256) xielu4_kernel(const T* __restrict__ z, in
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const float x = v[u];
-      o[u] = c + u < F ? (x > 0.f ? fmaf(ap * x, x, 0.5f * x) : fmaf(an, expm1f(x) - x, 0.5f * x)) : 0.f;
+      // bf16 activations: e^x - 1 from the fast exponential (its absolute error is far below the output's rounding step)
+      const float em1 = sizeof(T) == 2 ? __expf(x) - 1.f : expm1f(x);
+      o[u] = c + u < F ? (x > 0.f ? fmaf(ap * x, x, 0.5f * x) : fmaf(an, em1 - x, 0.5f * x)) : 0.f;
     }
     Vec4<T>::store(out + r * ldo + c, o);
   }
@@ -396,7 +398,8 @@ extern "C" int evo_xielu(const void* z, int64_t ldz, const void* coef, void* out
   const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)device_sm_count() * 16);
   cudaStream_t st = (cudaStream_t)stream;
   if (ldz % 4 == 0 && ldo % 4 == 0 && ldz >= (F + 3) / 4 * 4 && (dtype ? aligned4<float>(z) && aligned4<float>(out) : aligned4<bf16>(z) && aligned4<bf16>(out))) {
-    const dim3 g4((unsigned)((ldo / 4 + 255) / 256), (unsigned)std::min<int64_t>(rows, 32768));
+    // a thread walks several rows of its four columns, so that the two softplus of the coefficients are paid once per many elements
+    const dim3 g4((unsigned)((ldo / 4 + 255) / 256), (unsigned)std::min<int64_t>(rows, std::max<int64_t>(1, (int64_t)device_sm_count() * 8 / ((ldo / 4 + 255) / 256))));
     if (dtype) xielu4_kernel<float><<<g4, 256, 0, st>>>((const float*)z, ldz, (const bf16*)coef, (float*)out, ldo, rows, F);
     else xielu4_kernel<bf16><<<g4, 256, 0, st>>>((const bf16*)z, ldz, (const bf16*)coef, (bf16*)out, ldo, rows, F);
     return check_launch("evo_xielu");
