@@ -1,8 +1,9 @@
 """Configuration of a Nelovik model: read from the checkpoint folder's config.json (keys as the checkpoints carry them).
 
 Every size comes from here or from a tensor's shape; nothing is specialised to one checkpoint.  A layer is one of
-  "delta" (also "delta_<n>": the same mechanism under another name, with its own sizes)   gated delta rule
-  "parallel"                                                                              pooled-window attention beside a state-space mixer
+  "delta"      gated delta rule
+  "parallel"   pooled-window attention beside a state-space mixer
+(a numbered name such as "delta_2" is the same mechanism with sizes of its own)
 and may or may not have a feed-forward.  `runs` is the execution order (one run per layer); caches and states are keyed by run."""
 from __future__ import annotations
 
@@ -67,8 +68,10 @@ class Run:
     layer: int
 
 
-def _is_delta(kind: str) -> bool:
-    return kind == "delta" or (kind.startswith("delta_") and kind[len("delta_"):].isdigit())
+def _base_kind(kind: str) -> str:
+    """"delta_2" -> "delta": a numbered name is the same mechanism with sizes of its own."""
+    head, _, tail = kind.rpartition("_")
+    return head if head and tail.isdigit() else kind
 
 
 @dataclass
@@ -96,14 +99,14 @@ class NelovikConfig:
             if mlp is not None and mlp.get("kind", "dense") != "dense":
                 raise NotImplementedError(f"feed-forward kind {mlp.get('kind')!r}")
             ff = None if mlp is None else int(mlp["ff"])
-            if _is_delta(kind):
+            if _base_kind(kind) == "delta":
                 heads = int(m["heads"])
                 layers.append(LayerConfig("delta", delta=DeltaConfig(heads, int(m.get("kv_heads", heads)), int(m["dim"]), int(m["vdim"]), int(m["conv"])), ff=ff))
-            elif kind == "parallel":
+            elif _base_kind(kind) == "parallel":
                 a, s = m["left"], m["right"]
                 mask, rot = a.get("mask") or {}, a.get("rot") or {}
                 heads = int(a["heads"])
-                left = AttentionConfig(heads, int(a.get("kv_heads", heads)), int(a["dim"]), int(a["vdim"]), float(a["scale"]),
+                left = AttentionConfig(heads, int(a.get("kv_heads", heads)), int(a["dim"]), int(a["vdim"]), float(a.get("scale", int(a["dim"]) ** -0.5)),
                                        float(a.get("softcap", 0.0) or 0.0), int(mask.get("size", 0)), int(mask.get("pool", 0) or 0),
                                        int(rot.get("dims", 0) or 0), float(rot.get("base", 10000.0)))
                 if left.pool > 0 and left.window <= 0:

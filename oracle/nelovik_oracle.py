@@ -166,8 +166,9 @@ def feed_forward(h, w):
     return xielu(h @ w["up"].T, w["act"][0], w["act"][1]) @ w["down"].T
 
 
-def is_delta(kind: str) -> bool:
-    return kind == "delta" or (kind.startswith("delta_") and kind[len("delta_"):].isdigit())
+def base_kind(kind: str) -> str:
+    head, _, tail = kind.rpartition("_")
+    return head if head and tail.isdigit() else kind
 
 
 def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.float64, taps: Optional[list] = None) -> torch.Tensor:
@@ -180,9 +181,9 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
         mix = {k[len(p + "mix."):]: t for k, t in W.items() if k.startswith(p + "mix.")}
         h1 = rms(x, eps) * W[p + "norm1"]
         kind = layer["type"]
-        if is_delta(kind):
+        if base_kind(kind) == "delta":
             y = gated_delta(h1, mix, layer["mixer"], eps)
-        elif kind == "parallel":
+        elif base_kind(kind) == "parallel":
             y = parallel_mixer(h1, mix, layer["mixer"], eps)
         else:
             raise NotImplementedError(kind)
@@ -206,7 +207,7 @@ def make_config(width=48, vocab=61, layers=("parallel", "delta", "delta_2"), ff=
         if isinstance(kind, dict):
             out.append(kind)
             continue
-        if kind == "parallel":
+        if base_kind(kind) == "parallel":
             left = {"heads": att_heads, "kv_heads": att_kv_heads, "dim": att_dim, "vdim": att_vdim, "mask": {"size": window, "pool": pool},
                     "scale": scale, "softcap": softcap}
             if rot_dims:
@@ -224,7 +225,7 @@ def tensor_shapes(config: dict) -> Dict[str, tuple]:
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}.", layer["mixer"]
         out[p + "norm1"] = (d,)
-        if layer["type"] == "parallel":
+        if base_kind(layer["type"]) == "parallel":
             a, s = m["left"], m["right"]
             q = p + "mix.left."
             H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]

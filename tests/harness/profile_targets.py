@@ -84,4 +84,29 @@ elif what in ("movalorn", "movalorn_step"):
             d["mha"].seqlen_offset = d["hyena"].seqlen_offset = ctx + t
             lg, _ = model(nxt, inference_params_dict=d)
     torch.cuda.synchronize()
+elif what in ("nelovik", "nelovik_step"):
+    # a 2-layer Nelovik model (gated delta rule; pooled-window attention beside a state-space mixer) at width 2048: one prompt of
+    # 2 x 4096 tokens ("nelovik": every prompt kernel once per forward) or single-token steps of 16 sequences behind 2048 tokens
+    from evo_b200.nelovik import Nelovik, NelovikConfig
+    mlp = {"kind": "dense", "ff": 5632}
+    delta = {"type": "delta", "mixer": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}, "mlp": mlp}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": 1024, "pool": 64},
+                 "rot": {"dims": 64, "base": 10000.0}},
+        "right": {"heads": 32, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}}}
+    nc = {"architecture": "Nelovik", "vocab": 512, "width": 2048, "norm": {"eps": 1e-5}, "layers": [delta, par]}
+    model = Nelovik(NelovikConfig.from_dict(nc)).init_random(0, device=dev)
+    if what == "nelovik":
+        ids = torch.randint(0, 512, (2, 4096), device=dev)
+        for _ in range(2):
+            model(ids)
+    else:
+        B, ctx = 16, 2048
+        d = model.initialize_inference_params(max_seqlen=ctx + 64, max_batch_size=B)
+        lg, d = model(torch.randint(0, 512, (B, ctx), device=dev), inference_params_dict=d)
+        nxt = lg[:, -1].argmax(-1, keepdim=True)
+        for t in range(3):
+            d["mha"].seqlen_offset = d["hyena"].seqlen_offset = ctx + t
+            lg, _ = model(nxt, inference_params_dict=d)
+    torch.cuda.synchronize()
 print("done", what)
