@@ -4,6 +4,7 @@
 #include "common.cuh"
 #include "../../include/evo_b200.h"
 #include <math.h>
+#include <stdint.h>
 
 using namespace evo;
 
@@ -15,6 +16,25 @@ template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return _
 template <typename T> __device__ __forceinline__ void stf(T* p, float v);
 template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// four consecutive elements (16 bytes of fp32, 8 of bf16) as floats, and back
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float* o) { const float4 u = *reinterpret_cast<const float4*>(p); o[0] = u.x; o[1] = u.y; o[2] = u.z; o[3] = u.w; }
+  static __device__ __forceinline__ void store(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Vec4<bf16> {
+  static __device__ __forceinline__ void load(const bf16* p, float* o) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    o[0] = __uint_as_float(u.x << 16); o[1] = __uint_as_float(u.x & 0xffff0000u); o[2] = __uint_as_float(u.y << 16); o[3] = __uint_as_float(u.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(bf16* p, const float* v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 u; u.x = *reinterpret_cast<const uint32_t*>(&a); u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+template <typename T> inline bool aligned4(const void* p) { return !p || ((uintptr_t)p & (4 * sizeof(T) - 1)) == 0; }
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
@@ -80,6 +100,85 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(evo_qk_prep_params p) {
   }
 }
 
+// the same with four entries per access (head sizes, rotated halves, strides and bases multiples of four entries); the row's
+// sines and cosines are computed once and shared by all heads
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prep4_kernel(evo_qk_prep_params p) {
+  extern __shared__ __align__(16) float sm[];
+  const int qw = p.H * p.dk, kw = p.G * p.dk, vw = p.G * p.dv, half = p.rot_dims / 2;
+  float* qs = sm;              // [qw]
+  float* ks = qs + qw;         // [kw]
+  float* cs = ks + kw;         // [half] cosines, then [half] sines
+  float* red = cs + 2 * half + (4 - (2 * half) % 4) % 4;      // [33]
+  const int64_t row = blockIdx.x;
+  const int b = (int)(row / p.L);
+  const int64_t t = row - (int64_t)b * p.L;
+  const int64_t pos = (p.pos_dev ? *p.pos_dev : p.pos0) + t;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  T* q = (T*)p.q + row * p.ld;
+  const T* k = (const T*)p.k + row * p.ld;
+  const T* v = (const T*)p.v + row * p.ld;
+  T* crow = (T*)p.cache + (int64_t)b * p.cache_batch_stride + pos * p.cache_row;
+  const bf16* qb = (const bf16*)p.q_bias; const bf16* kb = (const bf16*)p.k_bias; const bf16* vb = (const bf16*)p.v_bias;
+  for (int e = tid; e < half; e += nt) sincosf((float)pos * p.freq[e], cs + half + e, cs + e);
+  float sq = 0.f, sk = 0.f;
+  for (int c = tid * 4; c < qw; c += nt * 4) {
+    float x[4], bb[4] = {0.f, 0.f, 0.f, 0.f};
+    Vec4<T>::load(q + c, x);
+    if (qb) Vec4<bf16>::load(qb + c, bb);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { x[u] += bb[u]; sq = fmaf(x[u], x[u], sq); }
+    Vec4<float>::store(qs + c, x);
+  }
+  for (int c = tid * 4; c < kw; c += nt * 4) {
+    float x[4], bb[4] = {0.f, 0.f, 0.f, 0.f};
+    Vec4<T>::load(k + c, x);
+    if (kb) Vec4<bf16>::load(kb + c, bb);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { x[u] += bb[u]; sk = fmaf(x[u], x[u], sk); }
+    Vec4<float>::store(ks + c, x);
+  }
+  for (int c = tid * 4; c < vw; c += nt * 4) {
+    float x[4], bb[4] = {0.f, 0.f, 0.f, 0.f};
+    Vec4<T>::load(v + c, x);
+    if (vb) Vec4<bf16>::load(vb + c, bb);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) x[u] += bb[u];
+    Vec4<T>::store(crow + kw + c, x);
+  }
+  const float rq = p.q_norm_w ? 1.0f / sqrtf(block_sum(sq, red) / (float)qw + p.eps) : 1.f;
+  const float rk = p.k_norm_w ? 1.0f / sqrtf(block_sum(sk, red) / (float)kw + p.eps) : 1.f;
+  if (!p.q_norm_w || !p.k_norm_w) __syncthreads();             // the staged rows and the table are complete
+  for (int part = 0; part < 2; ++part) {
+    const int width = part == 0 ? qw : kw;
+    const float* src = part == 0 ? qs : ks;
+    const bf16* nw = (const bf16*)(part == 0 ? p.q_norm_w : p.k_norm_w);
+    const float rs = part == 0 ? rq : rk;
+    T* dst = part == 0 ? q : crow;
+    for (int c = tid * 4; c < width; c += nt * 4) {
+      const int e = c % p.dk;                                    // the four entries lie in one head and on one side of every border
+      float x[4], w[4] = {1.f, 1.f, 1.f, 1.f};
+      Vec4<float>::load(src + c, x);
+      if (nw) Vec4<bf16>::load(nw + c, w);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) x[u] *= rs * w[u];
+      if (e < p.rot_dims) {
+        const int other = e < half ? c + half : c - half, a = e < half ? e : e - half;
+        float y[4], wo[4] = {1.f, 1.f, 1.f, 1.f};
+        Vec4<float>::load(src + other, y);
+        if (nw) Vec4<bf16>::load(nw + other, wo);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float o = y[u] * rs * wo[u];
+          // first half: u cos - v sin with v the partner; second half: v cos + u sin with u the partner
+          x[u] = e < half ? x[u] * cs[a + u] - o * cs[half + a + u] : x[u] * cs[a + u] + o * cs[half + a + u];
+        }
+      }
+      Vec4<T>::store(dst + c, x);
+    }
+  }
+}
+
 // grid (block slot, sequence): slot s is block pos / pool + s, done here iff its last row lies in [pos, pos + L)
 template <typename T>
 __global__ void __launch_bounds__(128) pool_rows_kernel(const T* __restrict__ cache, int64_t cache_row, int64_t cache_batch_stride, T* __restrict__ pooled,
@@ -108,9 +207,13 @@ extern "C" int evo_qk_prep(const evo_qk_prep_params* p, void* stream) {
   EVO_REQUIRE(p->rot_dims >= 0 && p->rot_dims <= p->dk && p->rot_dims % 2 == 0 && (p->rot_dims == 0 || p->freq), "evo_qk_prep: bad rotation (%d of %d)", p->rot_dims, p->dk);
   EVO_REQUIRE(p->cache_row >= (int64_t)p->G * (p->dk + p->dv), "evo_qk_prep: cache row too narrow");
   if (p->B == 0 || p->L == 0) return 0;
-  const size_t smem = sizeof(float) * ((size_t)(p->H + p->G) * p->dk + 33);
+  const size_t smem = sizeof(float) * ((size_t)(p->H + p->G) * p->dk + p->rot_dims + 4 + 33);
   EVO_REQUIRE(smem <= 200 * 1024, "evo_qk_prep: projections too wide for one CTA's shared memory");
-  auto kern = p->dtype ? qk_prep_kernel<float> : qk_prep_kernel<bf16>;
+  const bool al = p->dtype ? aligned4<float>(p->q) && aligned4<float>(p->k) && aligned4<float>(p->v) && aligned4<float>(p->cache)
+                           : aligned4<bf16>(p->q) && aligned4<bf16>(p->k) && aligned4<bf16>(p->v) && aligned4<bf16>(p->cache);
+  const bool vec = al && p->dk % 4 == 0 && p->dv % 4 == 0 && p->rot_dims % 8 == 0 && p->ld % 4 == 0 && p->cache_row % 4 == 0 && p->cache_batch_stride % 4 == 0 &&
+                   aligned4<bf16>(p->q_bias) && aligned4<bf16>(p->k_bias) && aligned4<bf16>(p->v_bias) && aligned4<bf16>(p->q_norm_w) && aligned4<bf16>(p->k_norm_w);
+  auto kern = p->dtype ? (vec ? qk_prep4_kernel<float> : qk_prep_kernel<float>) : (vec ? qk_prep4_kernel<bf16> : qk_prep_kernel<bf16>);
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<(unsigned)((int64_t)p->B * p->L), 256, smem, (cudaStream_t)stream>>>(*p);
   return check_launch("evo_qk_prep");

@@ -315,6 +315,39 @@ __global__ void __launch_bounds__(256) xielu4_kernel(const T* __restrict__ z, in
 }
 
 // ---- evo_gated_group_norm: one warp per (row, part)
+// the same with four entries per access (part size, strides and bases multiples of four entries)
+template <typename T>
+__global__ void __launch_bounds__(256) gated_group_norm4_kernel(const float* __restrict__ y, const T* __restrict__ gate, int64_t ldg, const bf16* __restrict__ nw,
+                                                                T* __restrict__ out, int64_t ldo, int64_t rows, int width, int groups, float eps) {
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= rows * groups) return;
+  const int64_t r = wid / groups; const int g = (int)(wid % groups);
+  const int gs = width / groups, c0 = g * gs;
+  const float* yr = y + r * width + c0;
+  const T* gr = gate + r * ldg + c0;
+  float ss = 0.f;
+  for (int c = lane * 4; c < gs; c += 128) {
+    float a[4], b[4];
+    Vec4<float>::load(yr + c, a); Vec4<T>::load(gr + c, b);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) { const float v = a[u] * silu_f(b[u]); ss = fmaf(v, v, ss); }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float rs = 1.0f / sqrtf(ss / (float)gs + eps);
+  T* orow = out + r * ldo;
+  for (int c = lane * 4; c < gs; c += 128) {
+    float a[4], b[4], w[4];
+    Vec4<float>::load(yr + c, a); Vec4<T>::load(gr + c, b); Vec4<bf16>::load(nw + c0 + c, w);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) a[u] = a[u] * silu_f(b[u]) * rs * w[u];
+    Vec4<T>::store(orow + c0 + c, a);
+  }
+  if (g == groups - 1)
+    for (int64_t c = width + lane; c < ldo; c += 32) stf(orow + c, 0.f);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int64_t ldg, const bf16* __restrict__ nw,
                                                                T* __restrict__ out, int64_t ldo, int64_t rows, int width, int groups, float eps) {
@@ -416,6 +449,12 @@ extern "C" int evo_gated_group_norm(const float* y, const void* gate, int64_t ld
   const int64_t warps = rows * groups;
   cudaStream_t st = (cudaStream_t)stream;
   const unsigned grid = (unsigned)((warps + 7) / 8);
+  if ((width / groups) % 4 == 0 && ldg % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)y & 15) == 0 && aligned4<bf16>(norm_w) &&
+      (dtype ? aligned4<float>(gate) && aligned4<float>(out) : aligned4<bf16>(gate) && aligned4<bf16>(out))) {
+    if (dtype) gated_group_norm4_kernel<float><<<grid, 256, 0, st>>>(y, (const float*)gate, ldg, (const bf16*)norm_w, (float*)out, ldo, rows, width, groups, eps);
+    else gated_group_norm4_kernel<bf16><<<grid, 256, 0, st>>>(y, (const bf16*)gate, ldg, (const bf16*)norm_w, (bf16*)out, ldo, rows, width, groups, eps);
+    return check_launch("evo_gated_group_norm");
+  }
   if (dtype) gated_group_norm_kernel<float><<<grid, 256, 0, st>>>(y, (const float*)gate, ldg, (const bf16*)norm_w, (float*)out, ldo, rows, width, groups, eps);
   else gated_group_norm_kernel<bf16><<<grid, 256, 0, st>>>(y, (const bf16*)gate, ldg, (const bf16*)norm_w, (bf16*)out, ldo, rows, width, groups, eps);
   return check_launch("evo_gated_group_norm");
