@@ -4,7 +4,9 @@
 // with everything around them that the recurrence consumes computed here in fp32 from the activated projections: the unit norms of
 // q and k, sigmoid / softplus / exponentials of the per-head gates, and for the delta rule the head's RMS norm, weight and SiLU gate.
 //
-// One CTA per (head, sequence, group of value channels).  Column j of the state belongs to LPC adjacent lanes of one warp, each
+// One CTA per (head, sequence, group of value channels).  A thread owns CPT (two, when the registers allow) adjacent columns:
+// every (key, query) pair read from shared memory then serves two columns, and the shared-memory pipe -- which bounded the
+// one-column form at half its time -- sees half the traffic per multiply-add.  Column j of the state belongs to LPC adjacent lanes of one warp, each
 // holding RPT rows in pairs (lane l, pair r: rows 2*(r*LPC + l) and + 1, so that the lanes of a column read consecutive 16-byte
 // (key, query, key, query) entries of shared memory, without bank conflicts); column sums (S^T k, S^T q) are folded with shuffles, so the time loop has no
 // barrier.  Value channels are independent in both recurrences: a head whose state does not fit one CTA's registers, or a call
@@ -55,8 +57,9 @@ struct ScanArgs {
   int B; int64_t L; int H, G, dk, dv;
 };
 
-template <typename T, int RPT, int MODE>
-__global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) matrix_state_kernel(ScanArgs p, int LPC, int dvp) {
+template <typename T, int RPT, int LPC, int MODE>
+__global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) matrix_state_kernel(ScanArgs p, int dvp) {
+  constexpr int CPT = RPT <= 16 ? 2 : 1;                   // columns per thread
   extern __shared__ __align__(16) float smem[];
   const int dk = p.dk, dv = p.dv, dkp = LPC * RPT;
   float2* kq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]   (key, query) per state row
@@ -66,8 +69,7 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
   const int h = blockIdx.x, b = blockIdx.y, g = h / (p.H / p.G);
   const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nw = nthr >> 5;
   const int j0 = blockIdx.z * dvp;                         // first value channel of this CTA
-  const int jl = tid / LPC, l = tid % LPC, j = j0 + jl;
-  const bool live = j < dv;
+  const int jl = (tid / LPC) * CPT, l = tid % LPC, j = j0 + jl;      // first of the thread's columns, within the CTA and within the head
   const T* kp = (const T*)p.kk + (int64_t)g * dk;
   const T* qp = (const T*)p.qq + (int64_t)g * dk;
   const T* vp = (const T*)p.vv + (int64_t)h * dv;
@@ -76,12 +78,14 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
   const float dtb = __bfloat162float(((const bf16*)p.dt_bias)[h]);
   const float Dh = MODE == MODE_SSD ? __bfloat162float(((const bf16*)p.Dskip)[h]) : 0.f;
 
-  float S[RPT];
+  float S[CPT][RPT];
 #pragma unroll
-  for (int r = 0; r < RPT; ++r) {
-    const int k = 2 * ((r >> 1) * LPC + l) + (r & 1);
-    S[r] = (Sg && !p.zero_start && live && k < dk) ? Sg[(int64_t)k * dv + j] : 0.f;
-  }
+  for (int c = 0; c < CPT; ++c)
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const int k = 2 * ((r >> 1) * LPC + l) + (r & 1);
+      S[c][r] = (Sg && !p.zero_start && j + c < dv && k < dk) ? Sg[(int64_t)k * dv + j + c] : 0.f;
+    }
 
   for (int64_t t0 = 0; t0 < p.L; t0 += TCH) {
     const int nt = (int)min((int64_t)TCH, p.L - t0);
@@ -123,40 +127,72 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
     __syncthreads();
     // ---- time loop
     for (int tt = 0; tt < nt; ++tt) {
-      const float v = vs[tt * dvp + jl];
+      float v[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) v[c] = vs[tt * dvp + jl + c];
       const float dec = sc[tt * 4 + 0];
       const float4* e = reinterpret_cast<const float4*>(kq + tt * dkp) + l;             // two state rows per 16-byte read; pair r at e[r * LPC]
       if (MODE == MODE_DELTA) {
-        float pk = 0.f, pq = 0.f;
+        constexpr bool KEEP = RPT <= 16;                   // the keys stay in registers for the update, or are read again
+        float pk[CPT], pq[CPT], kx[KEEP ? RPT : 2];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) pk[c] = pq[c] = 0.f;
 #pragma unroll
         for (int r = 0; r < RPT / 2; ++r) {
           const float4 f = e[r * LPC];
-          S[2 * r] *= dec;          pk = fmaf(S[2 * r], f.x, pk);     pq = fmaf(S[2 * r], f.y, pq);
-          S[2 * r + 1] *= dec;      pk = fmaf(S[2 * r + 1], f.z, pk); pq = fmaf(S[2 * r + 1], f.w, pq);
-        }
-        for (int o = 1; o < LPC; o <<= 1) { pk += __shfl_xor_sync(0xffffffffu, pk, o); pq += __shfl_xor_sync(0xffffffffu, pq, o); }
-        const float u = sc[tt * 4 + 1] * (v - pk);
+          if (KEEP) { kx[2 * r] = f.x; kx[2 * r + 1] = f.z; }
 #pragma unroll
-        for (int r = 0; r < RPT / 2; ++r) {
-          const float4 f = e[r * LPC];
-          S[2 * r] = fmaf(f.x, u, S[2 * r]);
-          S[2 * r + 1] = fmaf(f.z, u, S[2 * r + 1]);
+          for (int c = 0; c < CPT; ++c) {
+            S[c][2 * r] *= dec;          pk[c] = fmaf(S[c][2 * r], f.x, pk[c]);     pq[c] = fmaf(S[c][2 * r], f.y, pq[c]);
+            S[c][2 * r + 1] *= dec;      pk[c] = fmaf(S[c][2 * r + 1], f.z, pk[c]); pq[c] = fmaf(S[c][2 * r + 1], f.w, pq[c]);
+          }
         }
-        const float o = fmaf(u, sc[tt * 4 + 2], pq);
-        if (l == 0) {
-          if (p.y) { if (live) p.y[((row0 + tt) * p.H + h) * dv + j] = o; }
-          else os[tt * dvp + jl] = o;
+#pragma unroll
+        for (int o = 1; o < LPC; o <<= 1)
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) { pk[c] += __shfl_xor_sync(0xffffffffu, pk[c], o); pq[c] += __shfl_xor_sync(0xffffffffu, pq[c], o); }
+        const float beta = sc[tt * 4 + 1], kqd = sc[tt * 4 + 2];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+          const float u = beta * (v[c] - pk[c]);
+          if (KEEP) {
+#pragma unroll
+            for (int r = 0; r < RPT; ++r) S[c][r] = fmaf(kx[r], u, S[c][r]);
+          } else {
+#pragma unroll
+            for (int r = 0; r < RPT / 2; ++r) {
+              const float4 f = e[r * LPC];
+              S[c][2 * r] = fmaf(f.x, u, S[c][2 * r]);
+              S[c][2 * r + 1] = fmaf(f.z, u, S[c][2 * r + 1]);
+            }
+          }
+          const float o = fmaf(u, kqd, pq[c]);
+          if (l == 0) {
+            if (p.y) { if (j + c < dv) p.y[((row0 + tt) * p.H + h) * dv + j + c] = o; }
+            else os[tt * dvp + jl + c] = o;
+          }
         }
       } else {
-        float y = 0.f;
+        float y[CPT];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) y[c] = 0.f;
 #pragma unroll
         for (int r = 0; r < RPT / 2; ++r) {
           const float4 f = e[r * LPC];
-          S[2 * r] = fmaf(dec, S[2 * r], f.x * v);          y = fmaf(S[2 * r], f.y, y);
-          S[2 * r + 1] = fmaf(dec, S[2 * r + 1], f.z * v);  y = fmaf(S[2 * r + 1], f.w, y);
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) {
+            S[c][2 * r] = fmaf(dec, S[c][2 * r], f.x * v[c]);          y[c] = fmaf(S[c][2 * r], f.y, y[c]);
+            S[c][2 * r + 1] = fmaf(dec, S[c][2 * r + 1], f.z * v[c]);  y[c] = fmaf(S[c][2 * r + 1], f.w, y[c]);
+          }
         }
-        for (int o = 1; o < LPC; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-        if (l == 0 && live) p.y[((row0 + tt) * p.H + h) * dv + j] = fmaf(sc[tt * 4 + 1], v, y);
+#pragma unroll
+        for (int o = 1; o < LPC; o <<= 1)
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) y[c] += __shfl_xor_sync(0xffffffffu, y[c], o);
+        const float Dv = sc[tt * 4 + 1];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+          if (l == 0 && j + c < dv) p.y[((row0 + tt) * p.H + h) * dv + j + c] = fmaf(Dv, v[c], y[c]);
       }
     }
     if (MODE == MODE_DELTA && !p.y) {
@@ -180,12 +216,14 @@ __global__ void __launch_bounds__(RPT <= 8 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
       }
     }
   }
-  if (Sg && live) {
+  if (Sg) {
 #pragma unroll
-    for (int r = 0; r < RPT; ++r) {
-      const int k = 2 * ((r >> 1) * LPC + l) + (r & 1);
-      if (k < dk) Sg[(int64_t)k * dv + j] = S[r];
-    }
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        const int k = 2 * ((r >> 1) * LPC + l) + (r & 1);
+        if (k < dk && j + c < dv) Sg[(int64_t)k * dv + j + c] = S[c][r];
+      }
   }
 }
 
@@ -213,30 +251,33 @@ __global__ void __launch_bounds__(256) delta_head_norm_kernel(ScanArgs p) {
 }
 
 struct Plan { int rpt, lpc, dvc, chunks; };
-inline int thread_limit(int rpt) { return rpt <= 8 ? 1024 : (rpt <= 32 ? 512 : 256); }      // registers: rpt state rows per thread
+inline int thread_limit(int rpt) { return rpt <= 4 ? 1024 : (rpt <= 32 ? 512 : 256); }      // registers: rpt state rows per column per thread
+inline int columns_per_thread(int rpt) { return rpt <= 16 ? 2 : 1; }
 // about 8 lanes per column (three shuffle steps per fold), RPT = rows / lanes; the value channels a CTA takes follow from its
 // thread limit, and long calls on few (head, sequence) pairs are spread further so that every SM has a CTA
 inline Plan plan(int dk, int dv, int64_t ctas, int64_t L) {
-  const int dvp = (dv + 31) / 32 * 32;
   int rpt = 4;
   while (rpt < 64 && rpt * 8 < dk) rpt <<= 1;
   int lpc = 1;
   while (lpc * rpt < dk) lpc <<= 1;
   if (lpc > 32) return {0, 0, 0, 0};
-  const int per_cta = thread_limit(rpt) / lpc / 32 * 32;             // whole warps of columns
-  if (per_cta < 32) return {0, 0, 0, 0};
+  const int cpt = columns_per_thread(rpt);
+  const int gran = std::max(cpt, 32 * cpt / lpc);                    // columns of one warp: a CTA takes whole warps
+  const int dvp = (dv + gran - 1) / gran * gran;
+  const int per_cta = thread_limit(rpt) / 32 * gran;
   int chunks = (dvp + per_cta - 1) / per_cta;
-  if (L >= 256 && ctas * chunks * 2 <= device_sm_count()) chunks = (int)std::min<int64_t>(dvp / 32, device_sm_count() / ctas);
-  const int dvc = (dvp / 32 + chunks - 1) / chunks * 32;
+  if (L >= 256)
+    while (ctas * chunks < device_sm_count() && (dvp / gran + 2 * chunks - 1) / (2 * chunks) * gran >= 64 && 2 * chunks <= dvp / gran) chunks *= 2;   // a CTA keeps >= 64 columns: each one stages the head's keys and queries again
+  const int dvc = (dvp / gran + chunks - 1) / chunks * gran;
   return {rpt, lpc, dvc, (dv + dvc - 1) / dvc};
 }
 
-template <typename T, int RPT, int MODE>
+template <typename T, int RPT, int LPC, int MODE>
 int launch(const ScanArgs& a, const Plan& pl, cudaStream_t st, const char* what) {
-  const size_t smem = sizeof(float) * ((size_t)2 * TCH * pl.lpc * RPT + (size_t)2 * TCH * pl.dvc + (size_t)TCH * 4);
-  auto kern = matrix_state_kernel<T, RPT, MODE>;
+  const size_t smem = sizeof(float) * ((size_t)2 * TCH * LPC * RPT + (size_t)2 * TCH * pl.dvc + (size_t)TCH * 4);
+  auto kern = matrix_state_kernel<T, RPT, LPC, MODE>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<dim3(a.H, a.B, pl.chunks), dim3(pl.lpc * pl.dvc), smem, st>>>(a, pl.lpc, pl.dvc);
+  kern<<<dim3(a.H, a.B, pl.chunks), dim3(LPC * pl.dvc / columns_per_thread(RPT)), smem, st>>>(a, pl.dvc);
   int rc = check_launch(what);
   if (rc || MODE != MODE_DELTA || !a.y) return rc;
   const int64_t warps = (int64_t)a.B * a.L * a.H;
@@ -253,13 +294,21 @@ int dispatch(ScanArgs a, void* workspace, size_t workspace_bytes, cudaStream_t s
     if (!workspace || workspace_bytes < need) { set_error("%s: workspace too small (%zu < %zu)", what, workspace_bytes, need); return -1; }
     a.y = (float*)workspace;
   }
-  switch (pl.rpt) {
-    case 4: return launch<T, 4, MODE>(a, pl, st, what);
-    case 8: return launch<T, 8, MODE>(a, pl, st, what);
-    case 16: return launch<T, 16, MODE>(a, pl, st, what);
-    case 32: return launch<T, 32, MODE>(a, pl, st, what);
-    default: return launch<T, 64, MODE>(a, pl, st, what);
+  // the (rows per lane, lanes per column) pairs plan() can return: both are compile-time constants of the time loop
+  switch (pl.rpt * 100 + pl.lpc) {
+    case 401: return launch<T, 4, 1, MODE>(a, pl, st, what);
+    case 402: return launch<T, 4, 2, MODE>(a, pl, st, what);
+    case 404: return launch<T, 4, 4, MODE>(a, pl, st, what);
+    case 408: return launch<T, 4, 8, MODE>(a, pl, st, what);
+    case 808: return launch<T, 8, 8, MODE>(a, pl, st, what);
+    case 1608: return launch<T, 16, 8, MODE>(a, pl, st, what);
+    case 3208: return launch<T, 32, 8, MODE>(a, pl, st, what);
+    case 6408: return launch<T, 64, 8, MODE>(a, pl, st, what);
+    case 6416: return launch<T, 64, 16, MODE>(a, pl, st, what);
+    case 6432: return launch<T, 64, 32, MODE>(a, pl, st, what);
   }
+  set_error("%s: no kernel for %d rows per lane x %d lanes", what, pl.rpt, pl.lpc);
+  return -1;
 }
 
 }  // namespace
