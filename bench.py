@@ -649,7 +649,7 @@ def _nelovik_models(size, dev):
     mlp = {"kind": "dense", "ff": ff}
     delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "conv": 4}, "mlp": mlp}
     par = {"type": "parallel", "mlp": mlp, "mixer": {
-        "left": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": 1024, "pool": 64},
+        "left": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0, "mask": {"size": 1024, "pool": 64},
                  "rot": {"dims": 64, "base": 10000.0}},
         "right": {"heads": d // 64, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}}}
     nc = {"architecture": "Nelovik", "vocab": 512, "width": d, "norm": {"eps": 1e-5}, "layers": [delta, par, delta, delta]}

@@ -91,7 +91,7 @@ elif what in ("nelovik", "nelovik_step"):
     mlp = {"kind": "dense", "ff": 5632}
     delta = {"type": "delta", "mixer": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}, "mlp": mlp}
     par = {"type": "parallel", "mlp": mlp, "mixer": {
-        "left": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0, "mask": {"size": 1024, "pool": 64},
+        "left": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0, "mask": {"size": 1024, "pool": 64},
                  "rot": {"dims": 64, "base": 10000.0}},
         "right": {"heads": 32, "vdim": 64, "state": 128, "groups": 8, "norm_groups": 8, "conv": 4}}}
     nc = {"architecture": "Nelovik", "vocab": 512, "width": 2048, "norm": {"eps": 1e-5}, "layers": [delta, par]}
