@@ -1,5 +1,5 @@
 """Shared base of the model families that keep the residual stream in fp32 and are described by a flat table of checkpoint
-tensors (Zaverax, Movalorn): weight holding and strict loading, the padded GEMM weights, the linear-layer dispatch
+tensors (Zaverax, Movalorn, Nelovik): weight holding and strict loading, the padded GEMM weights, the linear-layer dispatch
 (tcgen05 GEMMs for bf16 activations, the CUDA-core fp32 GEMM for the all-fp32 mode), the inference-state holders, the
 forward protocol and the on-device generation loop.  A family provides `_ensure_packed()` and
 `_body(ids, B, L, state, offset, pos_dev=None, rows=None) -> fp32 logits`; everything that drives a model -- the generation loop,
