@@ -410,6 +410,8 @@ CONFIGS = {
                         kv_heads=2, att_kv_heads=4),
     "no_ff_no_pool": dict(layers=("parallel", "delta"), no_ff_layers=(0, 1), pool=0, rot_dims=0, softcap=0.0, taps=1, ssd_taps=1, heads=1, kv_heads=1, att_heads=1, att_kv_heads=1,
                           ssd_heads=1, groups=1, norm_groups=1),
+    "odd": dict(layers=("delta", "parallel", "delta_2"), width=50, ff=37, vocab=33, heads=3, kv_heads=1, dim=5, vdim=7, taps=2, att_heads=3, att_kv_heads=1, att_dim=10, att_vdim=9,
+                window=7, pool=2, rot_dims=6, ssd_heads=3, ssd_vdim=5, state=7, groups=1, norm_groups=3, ssd_taps=3),
     "wide": dict(layers=("parallel", "delta"), width=200, ff=264, heads=2, kv_heads=2, dim=72, vdim=136, taps=4, att_heads=2, att_kv_heads=1, att_dim=72, att_vdim=40, window=1000, pool=16,
                  rot_dims=72, ssd_heads=2, ssd_vdim=136, state=70, groups=2, norm_groups=2, ssd_taps=4),
 }
