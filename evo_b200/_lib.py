@@ -97,7 +97,7 @@ class WindowAttnParams(C.Structure):
                 ("q_pos0", C.c_int64), ("pos_dev", C.c_void_p), ("window", C.c_int64), ("keep_first", C.c_int64),
                 ("scale", C.c_float), ("lambda_", C.c_float), ("head_norm", C.c_int), ("norm_eps", C.c_float), ("out_scale", C.c_float), ("gate_per_head", C.c_int),
                 ("softcap", C.c_float), ("sink", C.c_void_p), ("pool", C.c_int64), ("pool_k", C.c_void_p), ("pool_v", C.c_void_p),
-                ("pool_tok_stride", C.c_int64), ("pool_batch_stride", C.c_int64)]
+                ("pool_tok_stride", C.c_int64), ("pool_batch_stride", C.c_int64), ("dist_r1", C.c_void_p), ("dist_r2", C.c_void_p)]
 
 
 class BranchNormParams(C.Structure):
@@ -168,7 +168,34 @@ class QkPrepParams(C.Structure):
                 ("q_norm_w", C.c_void_p), ("k_norm_w", C.c_void_p), ("eps", C.c_float), ("freq", C.c_void_p), ("rot_dims", C.c_int),
                 ("cache", C.c_void_p), ("cache_row", C.c_int64), ("cache_batch_stride", C.c_int64),
                 ("B", C.c_int), ("L", C.c_int64), ("H", C.c_int), ("G", C.c_int), ("dk", C.c_int), ("dv", C.c_int),
-                ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("dtype", C.c_int)]
+                ("pos0", C.c_int64), ("pos_dev", C.c_void_p), ("dtype", C.c_int),
+                ("norm_per_head", C.c_int), ("q_temp_coef", C.c_float), ("q_temp_every", C.c_int64)]
+
+
+class MoeRouteParams(C.Structure):
+    _fields_ = [("h", C.c_void_p), ("ldh", C.c_int64), ("router_w", C.c_void_p), ("correction", C.c_void_p),
+                ("weights", C.c_void_p), ("ldw", C.c_int64), ("chosen", C.c_void_p),
+                ("rows", C.c_int64), ("D", C.c_int), ("E", C.c_int), ("top", C.c_int), ("n_extra", C.c_int),
+                ("score_fn", C.c_int), ("groups", C.c_int), ("keep", C.c_int), ("normalize", C.c_int), ("norm_eps", C.c_float), ("scale", C.c_float), ("dtype", C.c_int)]
+
+
+class PostNormParams(C.Structure):
+    _fields_ = [("x", C.c_void_p), ("x_in", C.c_void_p),
+                ("y", C.c_void_p * 2), ("ldy", C.c_int64 * 2), ("scale", C.c_float * 2), ("n_in", C.c_int),
+                ("norm_w", C.c_void_p), ("norm_b", C.c_void_p), ("eps", C.c_float),
+                ("stack", C.c_void_p), ("stack_stride", C.c_int64), ("mix_n", C.c_int), ("mix_w", C.c_void_p),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("out_norm_w", C.c_void_p), ("out_norm_b", C.c_void_p),
+                ("dtype", C.c_int), ("rows", C.c_int64), ("D", C.c_int), ("gather", C.c_void_p)]
+
+
+class MlstmParams(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("ld", C.c_int64),
+                ("gi", C.c_void_p), ("gf", C.c_void_p), ("ldg", C.c_int64),
+                ("i_bias", C.c_void_p), ("f_bias", C.c_void_p), ("cap", C.c_float), ("q_scale", C.c_float), ("den_eps", C.c_float),
+                ("gate", C.c_void_p), ("ld_gate", C.c_int64), ("norm_w", C.c_void_p), ("eps", C.c_float),
+                ("state", C.c_void_p), ("mstate", C.c_void_p), ("zero_start", C.c_int),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("dtype", C.c_int),
+                ("B", C.c_int), ("L", C.c_int64), ("H", C.c_int), ("dk", C.c_int), ("dv", C.c_int)]
 
 
 # name -> (restype, argtypes); every symbol include/evo_b200.h declares
@@ -220,7 +247,7 @@ SIGNATURES = {
     "evo_embed_pair_f32": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_float,
                                      C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "evo_branch_norm": (C.c_int, [C.POINTER(BranchNormParams), C.c_void_p]),
-    "evo_glu_act": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "evo_glu_act": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "evo_scale_logits": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_void_p]),
     "evo_mingru_workspace": (C.c_size_t, [C.POINTER(MinGruParams)]),
     "evo_mingru_fwd": (C.c_int, [C.POINTER(MinGruParams), C.c_void_p, C.c_size_t, C.c_void_p]),
@@ -230,7 +257,7 @@ SIGNATURES = {
     "evo_moe_count": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "evo_moe_scatter": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "evo_gather_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
-    "evo_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
+    "evo_moe_combine": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "evo_sum_norm": (C.c_int, [C.POINTER(SumNormParams), C.c_void_p]),
     "evo_conv_act": (C.c_int, [C.POINTER(ConvActParams), C.c_void_p]),
@@ -241,6 +268,10 @@ SIGNATURES = {
     "evo_ssd_fwd": (C.c_int, [C.POINTER(SsdParams), C.c_void_p]),
     "evo_qk_prep": (C.c_int, [C.POINTER(QkPrepParams), C.c_void_p]),
     "evo_pool_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_void_p]),
+    "evo_moe_route_ex": (C.c_int, [C.POINTER(MoeRouteParams), C.c_void_p]),
+    "evo_post_norm": (C.c_int, [C.POINTER(PostNormParams), C.c_void_p]),
+    "evo_mlstm_workspace": (C.c_size_t, [C.POINTER(MlstmParams)]),
+    "evo_mlstm_fwd": (C.c_int, [C.POINTER(MlstmParams), C.c_void_p, C.c_size_t, C.c_void_p]),
     "evo_moe_route": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p]),
 }
 

@@ -15,7 +15,7 @@ LIB = os.path.join(HERE, "libevo_b200.so")
 SOURCES = ["api.cu", "elementwise.cu", "hyena.cu", "gemm_tcgen05.cu", "gemm_smallm.cu", "attention.cu", "attention_pp.cu", "decode.cu", "scoring.cu", "sampler.cu", "ingest.cu", "die_map.cu",
            "rowops.cu", "hgrn2.cu", "window_attention.cu", "window_attention_mma.cu", "gemm_simt.cu",
            "mingru.cu", "latent_attention.cu", "moe.cu",
-           "branch_ops.cu", "matrix_state.cu", "attention_prep.cu"]
+           "branch_ops.cu", "matrix_state.cu", "attention_prep.cu", "post_norm.cu"]
 # comparators for the GPU tests (cuBLASLt GEMM, CUDA-core attention): a separate library, never loaded by the product
 TEST_SRC = os.path.join(HERE, "..", "tests", "support", "test_support.cu")
 TEST_LIB = os.path.join(HERE, "..", "tests", "support", "libevo_b200_test.so")

@@ -1,4 +1,5 @@
-// Preparation of attention inputs whose query and key are normed over the whole projection and rotated in part (evo_qk_prep), and
+// Preparation of attention inputs whose query and key are normed (over the whole projection, or head by head), rotated in part and, for
+// the query, scaled by a temperature that grows with the position (evo_qk_prep), and
 // the pooled rows of a key/value cache (evo_pool_rows): the mean of every completed block of consecutive cache rows.
 // Biases, sums of squares, norms, angles and rotations are fp32; results are rounded once, when they are stored.
 #include "common.cuh"
@@ -53,6 +54,31 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[32];
 }
 
+// hr[0 .. H) and hr[H .. H + G): what every head's staged query / key entries are multiplied by -- the reciprocal root mean square of the
+// whole projection (sq, sk: this thread's part of its sum of squares) or of the head alone, and for the query the position's temperature
+__device__ __forceinline__ void head_scales(const evo_qk_prep_params& p, const float* qs, const float* ks, float sq, float sk, float* red, float* hr, int64_t pos) {
+  const int qw = p.H * p.dk, kw = p.G * p.dk;
+  const float temp = p.q_temp_every > 0 ? 1.f + p.q_temp_coef * logf((float)((pos + 1) / p.q_temp_every) + 1.f) : 1.f;
+  if (!p.norm_per_head) {
+    const float rq = p.q_norm_w ? 1.0f / sqrtf(block_sum(sq, red) / (float)qw + p.eps) : 1.f;
+    const float rk = p.k_norm_w ? 1.0f / sqrtf(block_sum(sk, red) / (float)kw + p.eps) : 1.f;
+    for (int i = threadIdx.x; i < p.H + p.G; i += blockDim.x) hr[i] = i < p.H ? rq * temp : rk;
+  } else {
+    __syncthreads();                                           // the staged rows are complete
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int i = w; i < p.H + p.G; i += nw) {
+      const float* src = i < p.H ? qs + i * p.dk : ks + (i - p.H) * p.dk;
+      float ss = 0.f;
+      for (int e = lane; e < p.dk; e += 32) ss = fmaf(src[e], src[e], ss);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const bool normed = i < p.H ? p.q_norm_w != nullptr : p.k_norm_w != nullptr;
+      if (lane == 0) hr[i] = (normed ? 1.0f / sqrtf(ss / (float)p.dk + p.eps) : 1.f) * (i < p.H ? temp : 1.f);
+    }
+  }
+  __syncthreads();
+}
+
 // one CTA per row: the biased q and k rows wait in shared memory for their sums of squares, then are normed, turned and stored
 template <typename T>
 __global__ void __launch_bounds__(256) qk_prep_kernel(evo_qk_prep_params p) {
@@ -61,6 +87,7 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(evo_qk_prep_params p) {
   float* qs = sm;              // [qw]
   float* ks = qs + qw;         // [kw]
   float* red = ks + kw;        // [33]
+  float* hr = red + 33;        // [H + G] reciprocal root mean squares, per head
   const int64_t row = blockIdx.x;
   const int b = (int)(row / p.L);
   const int64_t t = row - (int64_t)b * p.L;
@@ -75,8 +102,7 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(evo_qk_prep_params p) {
   for (int c = tid; c < qw; c += nt) { const float x = ldf(q + c) + (qb ? __bfloat162float(qb[c]) : 0.f); qs[c] = x; sq = fmaf(x, x, sq); }
   for (int c = tid; c < kw; c += nt) { const float x = ldf(k + c) + (kb ? __bfloat162float(kb[c]) : 0.f); ks[c] = x; sk = fmaf(x, x, sk); }
   for (int c = tid; c < vw; c += nt) stf(crow + kw + c, ldf(v + c) + (vb ? __bfloat162float(vb[c]) : 0.f));
-  const float rq = p.q_norm_w ? 1.0f / sqrtf(block_sum(sq, red) / (float)qw + p.eps) : 1.f;
-  const float rk = p.k_norm_w ? 1.0f / sqrtf(block_sum(sk, red) / (float)kw + p.eps) : 1.f;
+  head_scales(p, qs, ks, sq, sk, red, hr, pos);
   const bf16* qn = (const bf16*)p.q_norm_w; const bf16* kn = (const bf16*)p.k_norm_w;
   const int half = p.rot_dims / 2;
   // an entry is written by the thread that owns it; a turned pair (e, e + half) is owned by the thread of e
@@ -84,14 +110,15 @@ __global__ void __launch_bounds__(256) qk_prep_kernel(evo_qk_prep_params p) {
     const int width = part == 0 ? qw : kw;
     const float* src = part == 0 ? qs : ks;
     const bf16* nw = part == 0 ? qn : kn;
-    const float rs = part == 0 ? rq : rk;
+    const float* hrs = part == 0 ? hr : hr + p.H;
     T* dst = part == 0 ? q : crow;
     for (int c = tid; c < width; c += nt) {
-      const int e = c % p.dk;
-      if (e >= p.rot_dims) { stf(dst + c, src[c] * rs * (nw ? __bfloat162float(nw[c]) : 1.f)); continue; }
+      const int e = c % p.dk, wc = p.norm_per_head ? e : c;       // a per-head norm weight has dk entries
+      const float rs = hrs[c / p.dk];
+      if (e >= p.rot_dims) { stf(dst + c, src[c] * rs * (nw ? __bfloat162float(nw[wc]) : 1.f)); continue; }
       if (e >= half) continue;
-      const float u = src[c] * rs * (nw ? __bfloat162float(nw[c]) : 1.f);
-      const float w = src[c + half] * rs * (nw ? __bfloat162float(nw[c + half]) : 1.f);
+      const float u = src[c] * rs * (nw ? __bfloat162float(nw[wc]) : 1.f);
+      const float w = src[c + half] * rs * (nw ? __bfloat162float(nw[wc + half]) : 1.f);
       float sn, cs;
       sincosf((float)pos * p.freq[e], &sn, &cs);
       stf(dst + c, u * cs - w * sn);
@@ -110,6 +137,7 @@ __global__ void __launch_bounds__(256) qk_prep4_kernel(evo_qk_prep_params p) {
   float* ks = qs + qw;         // [kw]
   float* cs = ks + kw;         // [half] cosines, then [half] sines
   float* red = cs + 2 * half + (4 - (2 * half) % 4) % 4;      // [33]
+  float* hr = red + 33;                                        // [H + G] reciprocal root mean squares, per head
   const int64_t row = blockIdx.x;
   const int b = (int)(row / p.L);
   const int64_t t = row - (int64_t)b * p.L;
@@ -146,27 +174,27 @@ __global__ void __launch_bounds__(256) qk_prep4_kernel(evo_qk_prep_params p) {
     for (int u = 0; u < 4; ++u) x[u] += bb[u];
     Vec4<T>::store(crow + kw + c, x);
   }
-  const float rq = p.q_norm_w ? 1.0f / sqrtf(block_sum(sq, red) / (float)qw + p.eps) : 1.f;
-  const float rk = p.k_norm_w ? 1.0f / sqrtf(block_sum(sk, red) / (float)kw + p.eps) : 1.f;
-  if (!p.q_norm_w || !p.k_norm_w) __syncthreads();             // the staged rows and the table are complete
+  head_scales(p, qs, ks, sq, sk, red, hr, pos);                 // ends with a barrier: the staged rows and the table are complete
   for (int part = 0; part < 2; ++part) {
     const int width = part == 0 ? qw : kw;
     const float* src = part == 0 ? qs : ks;
     const bf16* nw = (const bf16*)(part == 0 ? p.q_norm_w : p.k_norm_w);
-    const float rs = part == 0 ? rq : rk;
+    const float* hrs = part == 0 ? hr : hr + p.H;
     T* dst = part == 0 ? q : crow;
     for (int c = tid * 4; c < width; c += nt * 4) {
       const int e = c % p.dk;                                    // the four entries lie in one head and on one side of every border
+      const int wo0 = p.norm_per_head ? e - c : 0;               // weight index = column + wo0 (a per-head weight has dk entries)
+      const float rs = hrs[c / p.dk];
       float x[4], w[4] = {1.f, 1.f, 1.f, 1.f};
       Vec4<float>::load(src + c, x);
-      if (nw) Vec4<bf16>::load(nw + c, w);
+      if (nw) Vec4<bf16>::load(nw + c + wo0, w);
 #pragma unroll
       for (int u = 0; u < 4; ++u) x[u] *= rs * w[u];
       if (e < p.rot_dims) {
         const int other = e < half ? c + half : c - half, a = e < half ? e : e - half;
         float y[4], wo[4] = {1.f, 1.f, 1.f, 1.f};
         Vec4<float>::load(src + other, y);
-        if (nw) Vec4<bf16>::load(nw + other, wo);
+        if (nw) Vec4<bf16>::load(nw + other + wo0, wo);
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const float o = y[u] * rs * wo[u];
@@ -207,7 +235,7 @@ extern "C" int evo_qk_prep(const evo_qk_prep_params* p, void* stream) {
   EVO_REQUIRE(p->rot_dims >= 0 && p->rot_dims <= p->dk && p->rot_dims % 2 == 0 && (p->rot_dims == 0 || p->freq), "evo_qk_prep: bad rotation (%d of %d)", p->rot_dims, p->dk);
   EVO_REQUIRE(p->cache_row >= (int64_t)p->G * (p->dk + p->dv), "evo_qk_prep: cache row too narrow");
   if (p->B == 0 || p->L == 0) return 0;
-  const size_t smem = sizeof(float) * ((size_t)(p->H + p->G) * p->dk + p->rot_dims + 4 + 33);
+  const size_t smem = sizeof(float) * ((size_t)(p->H + p->G) * p->dk + p->rot_dims + 4 + 33 + p->H + p->G);
   EVO_REQUIRE(smem <= 200 * 1024, "evo_qk_prep: projections too wide for one CTA's shared memory");
   const bool al = p->dtype ? aligned4<float>(p->q) && aligned4<float>(p->k) && aligned4<float>(p->v) && aligned4<float>(p->cache)
                            : aligned4<bf16>(p->q) && aligned4<bf16>(p->k) && aligned4<bf16>(p->v) && aligned4<bf16>(p->cache);

@@ -1,6 +1,7 @@
 // Recurrences whose state is a (dk x dv) matrix per head, carried in fp32 registers for the whole call:
 //   gated delta rule   S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q        (evo_gated_delta_fwd)
 //   state-space dual   S <- a S + (dt B) x^T;  y = S^T C + D x                             (evo_ssd_fwd)
+//   matrix memory      m' = max(f + m, i);  S <- e^{f+m-m'} S + e^{i-m'} k v^T;  n alike;  o = S^T q / (max(|n.q|, e^{-m'}) + c)   (evo_mlstm_fwd)
 // with everything around them that the recurrence consumes computed here in fp32 from the activated projections: the unit norms of
 // q and k, sigmoid / softplus / exponentials of the per-head gates, and for the delta rule the head's RMS norm, weight and SiLU gate.
 //
@@ -16,6 +17,8 @@
 // The delta rule needs S^T k before it can write: both products are taken from the decayed state in one pass,
 //   p = (gS)^T k,  r = (gS)^T q,  u = beta (v - p),  o = r + u (k . q),
 // and the rank-one update follows with u -- one shuffle fold per token instead of two.
+// The matrix memory's normaliser n is one more column of its state (a value channel that is always 1), so n.q falls out of the same loop;
+// its running maximum is a scalar scan over the round's tokens that one thread does between staging and the time loop.
 // The single-token step is the same kernel with L == 1.
 #include "common.cuh"
 #include "../../include/evo_b200.h"
@@ -41,7 +44,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 constexpr int TCH = 16;      // tokens staged per round
-enum { MODE_DELTA = 0, MODE_SSD = 1 };
+enum { MODE_DELTA = 0, MODE_SSD = 1, MODE_MLSTM = 2 };
 
 // what both recurrences look like to the time loop
 struct ScanArgs {
@@ -52,10 +55,16 @@ struct ScanArgs {
   float* state; int zero_start;
   // delta epilogue
   const void* gate; int64_t ldg; const void* norm_w; float eps; void* out; int64_t ldo;
-  // ssd output, or the delta rule's un-normed read-outs when a head is spread over several CTAs: (rows, H*dv) fp32
+  // ssd output, or the un-normed read-outs of the other two when a head is spread over several CTAs: (rows, H*dv) fp32
   float* y;
   int B; int64_t L; int H, G, dk, dv;
+  // matrix memory: dv counts the normaliser's column (dv_real value channels + 1); gate biases, soft cap, e^{-m} per (row, head) beside y
+  int dv_real; const void* i_bias; const void* f_bias; float cap, den_eps; float* mstate; float* em;
 };
+
+// soft cap c tanh(z / c) (c <= 0: none) and log sigmoid
+__device__ __forceinline__ float soft_cap(float z, float c) { return c > 0.f ? c * tanhf(z / c) : z; }
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
 template <typename T, int RPT, int LPC, int MODE>
 __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) matrix_state_kernel(ScanArgs p, int dvp) {
@@ -72,10 +81,11 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
   const int jl = (tid / LPC) * CPT, l = tid % LPC, j = j0 + jl;      // first of the thread's columns, within the CTA and within the head
   const T* kp = (const T*)p.kk + (int64_t)g * dk;
   const T* qp = (const T*)p.qq + (int64_t)g * dk;
-  const T* vp = (const T*)p.vv + (int64_t)h * dv;
+  const T* vp = (const T*)p.vv + (int64_t)h * (MODE == MODE_MLSTM ? p.dv_real : dv);
   float* Sg = p.state ? p.state + ((int64_t)b * p.H + h) * dk * (int64_t)dv : nullptr;
-  const float A = expf(__bfloat162float(((const bf16*)p.A_log)[h]));
-  const float dtb = __bfloat162float(((const bf16*)p.dt_bias)[h]);
+  const float A = MODE == MODE_MLSTM ? 0.f : expf(__bfloat162float(((const bf16*)p.A_log)[h]));
+  const float dtb = MODE == MODE_MLSTM ? 0.f : __bfloat162float(((const bf16*)p.dt_bias)[h]);
+  float mrun = (MODE == MODE_MLSTM && p.mstate && !p.zero_start) ? p.mstate[(int64_t)b * p.H + h] : 0.f;      // thread 0's: the running maximum
   const float Dh = MODE == MODE_SSD ? __bfloat162float(((const bf16*)p.Dskip)[h]) : 0.f;
 
   float S[CPT][RPT];
@@ -113,6 +123,18 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
           sc[tt * 4 + 1] = 1.f / (1.f + expf(-bv));
           sc[tt * 4 + 2] = skq * rk * rq;
         }
+      } else if (MODE == MODE_MLSTM) {
+        for (int e = lane; e < dkp; e += 32) {
+          float2 o = make_float2(0.f, 0.f);
+          if (e < dk) { o.x = ldf(kp + row * p.ld + e); o.y = ldf(qp + row * p.ld + e) * p.q_scale; }
+          kq[tt * dkp + e] = o;
+        }
+        if (lane == 0) {                                  // log forget gate, log input gate; the scan below turns them into factors
+          const float gi = ldf((const T*)p.s0 + row * p.lds + h) + __bfloat162float(((const bf16*)p.i_bias)[h]);
+          const float gf = ldf((const T*)p.s1 + row * p.lds + h) + __bfloat162float(((const bf16*)p.f_bias)[h]);
+          sc[tt * 4 + 0] = log_sigmoid(soft_cap(gf, p.cap));
+          sc[tt * 4 + 1] = soft_cap(gi, p.cap);
+        }
       } else {
         const float dt = softplus_f(ldf((const T*)p.s0 + row * p.lds + h) + dtb);
         for (int e = lane; e < dkp; e += 32) {
@@ -122,9 +144,27 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
         }
         if (lane == 0) { sc[tt * 4 + 0] = expf(-A * dt); sc[tt * 4 + 1] = Dh; }
       }
-      for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = j0 + c < dv ? ldf(vp + row * p.ld + j0 + c) : 0.f;
+      if (MODE == MODE_MLSTM) {
+        for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = j0 + c < p.dv_real ? ldf(vp + row * p.ld + j0 + c) : (j0 + c == p.dv_real ? 1.f : 0.f);
+      } else {
+        for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = j0 + c < dv ? ldf(vp + row * p.ld + j0 + c) : 0.f;
+      }
     }
     __syncthreads();
+    if (MODE == MODE_MLSTM) {
+      if (tid == 0) {
+        for (int tt = 0; tt < nt; ++tt) {
+          const float f = sc[tt * 4 + 0], i = sc[tt * 4 + 1];
+          const float mn = fmaxf(f + mrun, i);
+          sc[tt * 4 + 0] = expf(f + mrun - mn);
+          sc[tt * 4 + 1] = expf(i - mn);
+          sc[tt * 4 + 2] = expf(-mn);
+          if (p.em && blockIdx.z == 0) p.em[(row0 + tt) * p.H + h] = sc[tt * 4 + 2];
+          mrun = mn;
+        }
+      }
+      __syncthreads();
+    }
     // ---- time loop
     for (int tt = 0; tt < nt; ++tt) {
       float v[CPT];
@@ -176,6 +216,11 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
         float y[CPT];
 #pragma unroll
         for (int c = 0; c < CPT; ++c) y[c] = 0.f;
+        if (MODE == MODE_MLSTM) {
+          const float inn = sc[tt * 4 + 1];
+#pragma unroll
+          for (int c = 0; c < CPT; ++c) v[c] *= inn;
+        }
 #pragma unroll
         for (int r = 0; r < RPT / 2; ++r) {
           const float4 f = e[r * LPC];
@@ -189,10 +234,39 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
         for (int o = 1; o < LPC; o <<= 1)
 #pragma unroll
           for (int c = 0; c < CPT; ++c) y[c] += __shfl_xor_sync(0xffffffffu, y[c], o);
-        const float Dv = sc[tt * 4 + 1];
+        if (MODE == MODE_MLSTM) {
 #pragma unroll
-        for (int c = 0; c < CPT; ++c)
-          if (l == 0 && j + c < dv) p.y[((row0 + tt) * p.H + h) * dv + j + c] = fmaf(Dv, v[c], y[c]);
+          for (int c = 0; c < CPT; ++c)
+            if (l == 0) {
+              if (p.y) { if (j + c < dv) p.y[((row0 + tt) * p.H + h) * dv + j + c] = y[c]; }
+              else os[tt * dvp + jl + c] = y[c];
+            }
+        } else {
+          const float Dv = sc[tt * 4 + 1];
+#pragma unroll
+          for (int c = 0; c < CPT; ++c)
+            if (l == 0 && j + c < dv) p.y[((row0 + tt) * p.H + h) * dv + j + c] = fmaf(Dv, v[c], y[c]);
+        }
+      }
+    }
+    if (MODE == MODE_MLSTM && !p.y) {
+      __syncthreads();
+      // normaliser, head norm, weight over all heads, sigmoid gate, store: one warp per token
+      const bf16* nwt = (const bf16*)p.norm_w + (int64_t)h * p.dv_real;
+      const int dvr = p.dv_real;
+      for (int tt = warp; tt < nt; tt += nw) {
+        const int64_t row = row0 + tt;
+        const float inv = 1.f / (fmaxf(fabsf(os[tt * dvp + dvr]), sc[tt * 4 + 2]) + p.den_eps);
+        float ss = 0.f;
+        for (int c = lane; c < dvr; c += 32) { const float o = os[tt * dvp + c] * inv; ss = fmaf(o, o, ss); }
+        ss = warp_sum(ss);
+        const float rstd = inv / sqrtf(ss / (float)dvr + p.eps);
+        T* orow = (T*)p.out + row * p.ldo;
+        const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * dvr;
+        for (int c = lane; c < dvr; c += 32)
+          stf(orow + h * dvr + c, os[tt * dvp + c] * rstd * __bfloat162float(nwt[c]) / (1.f + expf(-ldf(grow + c))));
+        if (h == p.H - 1)
+          for (int64_t c = (int64_t)p.H * dvr + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
       }
     }
     if (MODE == MODE_DELTA && !p.y) {
@@ -216,6 +290,7 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
       }
     }
   }
+  if (MODE == MODE_MLSTM && p.mstate && tid == 0 && blockIdx.z == 0) p.mstate[(int64_t)b * p.H + h] = mrun;
   if (Sg) {
 #pragma unroll
     for (int c = 0; c < CPT; ++c)
@@ -250,6 +325,28 @@ __global__ void __launch_bounds__(256) delta_head_norm_kernel(ScanArgs p) {
     for (int64_t c = (int64_t)p.H * p.dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
 }
 
+// the same for the matrix memory's read-outs (rows, H, dv_real + 1) with e^{-m} beside them
+template <typename T>
+__global__ void __launch_bounds__(256) mlstm_head_norm_kernel(ScanArgs p) {
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (wid >= (int64_t)p.B * p.L * p.H) return;
+  const int64_t row = wid / p.H; const int h = (int)(wid % p.H);
+  const int dvr = p.dv_real;
+  const float* r = p.y + wid * p.dv;
+  const float inv = 1.f / (fmaxf(fabsf(r[dvr]), p.em[wid]) + p.den_eps);
+  float ss = 0.f;
+  for (int c = lane; c < dvr; c += 32) { const float o = r[c] * inv; ss = fmaf(o, o, ss); }
+  ss = warp_sum(ss);
+  const float rstd = inv / sqrtf(ss / (float)dvr + p.eps);
+  T* orow = (T*)p.out + row * p.ldo;
+  const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * dvr;
+  const bf16* nw = (const bf16*)p.norm_w + (int64_t)h * dvr;
+  for (int c = lane; c < dvr; c += 32) stf(orow + h * dvr + c, r[c] * rstd * __bfloat162float(nw[c]) / (1.f + expf(-ldf(grow + c))));
+  if (h == p.H - 1)
+    for (int64_t c = (int64_t)p.H * dvr + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+}
+
 struct Plan { int rpt, lpc, dvc, chunks; };
 inline int thread_limit(int rpt) { return rpt <= 4 ? 1024 : (rpt <= 32 ? 512 : 256); }      // registers: rpt state rows per column per thread
 inline int columns_per_thread(int rpt) { return rpt <= 16 ? 2 : 1; }
@@ -279,9 +376,10 @@ int launch(const ScanArgs& a, const Plan& pl, cudaStream_t st, const char* what)
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3(a.H, a.B, pl.chunks), dim3(LPC * pl.dvc / columns_per_thread(RPT)), smem, st>>>(a, pl.dvc);
   int rc = check_launch(what);
-  if (rc || MODE != MODE_DELTA || !a.y) return rc;
+  if (rc || MODE == MODE_SSD || !a.y) return rc;
   const int64_t warps = (int64_t)a.B * a.L * a.H;
-  delta_head_norm_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(a);
+  if (MODE == MODE_DELTA) delta_head_norm_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(a);
+  else mlstm_head_norm_kernel<T><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(a);
   return check_launch(what);
 }
 
@@ -289,10 +387,12 @@ template <typename T, int MODE>
 int dispatch(ScanArgs a, void* workspace, size_t workspace_bytes, cudaStream_t st, const char* what) {
   const Plan pl = plan(a.dk, a.dv, (int64_t)a.B * a.H, a.L);
   if (pl.rpt == 0) { set_error("%s: a state of %d rows per head does not fit (rows <= 2048)", what, a.dk); return -1; }
-  if (MODE == MODE_DELTA && pl.chunks > 1) {
-    const size_t need = sizeof(float) * (size_t)a.B * a.L * a.H * a.dv;
+  if (MODE != MODE_SSD && pl.chunks > 1) {
+    const size_t rows = (size_t)a.B * a.L * a.H;
+    const size_t need = sizeof(float) * rows * (a.dv + (MODE == MODE_MLSTM ? 1 : 0));
     if (!workspace || workspace_bytes < need) { set_error("%s: workspace too small (%zu < %zu)", what, workspace_bytes, need); return -1; }
     a.y = (float*)workspace;
+    if (MODE == MODE_MLSTM) a.em = a.y + rows * a.dv;
   }
   // the (rows per lane, lanes per column) pairs plan() can return: both are compile-time constants of the time loop
   switch (pl.rpt * 100 + pl.lpc) {
@@ -347,4 +447,32 @@ extern "C" int evo_ssd_fwd(const evo_ssd_params* p, void* stream) {
   a.y = p->y;
   a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->G; a.dk = p->N; a.dv = p->dv;
   return p->dtype ? dispatch<float, MODE_SSD>(a, nullptr, 0, (cudaStream_t)stream, "evo_ssd_fwd") : dispatch<bf16, MODE_SSD>(a, nullptr, 0, (cudaStream_t)stream, "evo_ssd_fwd");
+}
+
+namespace {
+inline ScanArgs mlstm_args(const evo_mlstm_params* p) {
+  ScanArgs a = {};
+  a.kk = p->k; a.qq = p->q; a.vv = p->v; a.ld = p->ld;
+  a.s0 = p->gi; a.s1 = p->gf; a.lds = p->ldg;
+  a.i_bias = p->i_bias; a.f_bias = p->f_bias; a.cap = p->cap; a.den_eps = p->den_eps; a.q_scale = p->q_scale;
+  a.state = p->state; a.mstate = p->mstate; a.zero_start = p->zero_start;
+  a.gate = p->gate; a.ldg = p->ld_gate; a.norm_w = p->norm_w; a.eps = p->eps; a.out = p->out; a.ldo = p->ldo;
+  a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->H; a.dk = p->dk; a.dv = p->dv + 1; a.dv_real = p->dv;
+  return a;
+}
+}  // namespace
+
+extern "C" size_t evo_mlstm_workspace(const evo_mlstm_params* p) {
+  const Plan pl = plan(p->dk, p->dv + 1, (int64_t)p->B * p->H, p->L);
+  return pl.chunks > 1 ? sizeof(float) * (size_t)p->B * p->L * p->H * (p->dv + 2) : 0;
+}
+
+extern "C" int evo_mlstm_fwd(const evo_mlstm_params* p, void* workspace, size_t workspace_bytes, void* stream) {
+  EVO_REQUIRE(p->q && p->k && p->v && p->gi && p->gf && p->i_bias && p->f_bias && p->gate && p->norm_w && p->out, "evo_mlstm_fwd: null argument");
+  EVO_REQUIRE((p->state == nullptr) == (p->mstate == nullptr), "evo_mlstm_fwd: the matrix state and the running maximum come together");
+  EVO_REQUIRE(p->B >= 0 && p->L >= 0 && p->H > 0 && p->dk > 0 && p->dv > 0 && p->ldo >= (int64_t)p->H * p->dv, "evo_mlstm_fwd: bad shape");
+  if (p->B == 0 || p->L == 0) return 0;
+  const ScanArgs a = mlstm_args(p);
+  return p->dtype ? dispatch<float, MODE_MLSTM>(a, workspace, workspace_bytes, (cudaStream_t)stream, "evo_mlstm_fwd")
+                  : dispatch<bf16, MODE_MLSTM>(a, workspace, workspace_bytes, (cudaStream_t)stream, "evo_mlstm_fwd");
 }

@@ -550,18 +550,20 @@ __device__ __forceinline__ float act_value(float z, int act) {
     if (sizeof(T) == 4) return 0.5f * z * (1.f + tanhf(a));
     return z * sigm<T>(2.f * a);
   }
+  if (act == 2) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));     // erf form of gelu
   return z * sigm<T>(z);                   // silu
 }
 
-// out[r, c] = act(g[r, c]) * u[r, c] * w(r, c) for c < F, zero for F <= c < ldo;  w = group_w[r, c / group] for c < n_groups * group, else 1.
+// out[r, c] = act(g[r, c]) * u[r, c] * w(r, c) for c < F, zero for F <= c < ldo (u == nullptr: no second factor);
+// w = group_w[r * ldw + c / group] for c < n_groups * group, after them group_w[r * ldw + n_groups] with tail_w, else 1.
 // grid (rows, column chunks): few rows (a decoding step) still fill the GPU.  VEC: 4 columns per thread (F, group, strides multiples of 4).
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(256) glu_act_kernel(const T* __restrict__ g, const T* __restrict__ u, int64_t ld, T* __restrict__ out, int64_t ldo,
-                                                      int F, int act, const float* __restrict__ group_w, int group, int n_groups) {
+                                                      int F, int act, const float* __restrict__ group_w, int64_t ldw, int group, int n_groups, int tail_w) {
   const int64_t r = blockIdx.x;
-  const T* gr = g + r * ld; const T* ur = u + r * ld;
+  const T* gr = g + r * ld; const T* ur = u ? u + r * ld : nullptr;
   T* orow = out + r * ldo;
-  const float* wr = group_w ? group_w + r * n_groups : nullptr;
+  const float* wr = group_w ? group_w + r * ldw : nullptr;
   constexpr int VW = VEC ? 4 : 1;
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VW;
   if (c >= ldo) return;
@@ -570,14 +572,14 @@ __global__ void __launch_bounds__(256) glu_act_kernel(const T* __restrict__ g, c
   for (int k = 0; k < VW; ++k) v[k] = 0.f;
   if (c < F) {
     float wt = 1.f;
-    if (wr) { const int e = c / group; if (e < n_groups) wt = wr[e]; }
+    if (wr) { const int e = c / group; if (e < n_groups) wt = wr[e]; else if (tail_w) wt = wr[n_groups]; }
     if (wt != 0.f) {
       if (VEC) {
-        const float4 g4 = ld4(gr + c), u4 = ld4(ur + c);
+        const float4 g4 = ld4(gr + c), u4 = ur ? ld4(ur + c) : make_float4(1.f, 1.f, 1.f, 1.f);
         v[0] = act_value<T>(g4.x, act) * u4.x * wt; v[1] = act_value<T>(g4.y, act) * u4.y * wt;
         v[2] = act_value<T>(g4.z, act) * u4.z * wt; v[3] = act_value<T>(g4.w, act) * u4.w * wt;
       } else {
-        v[0] = act_value<T>(ldf(gr + c), act) * ldf(ur + c) * wt;
+        v[0] = act_value<T>(ldf(gr + c), act) * (ur ? ldf(ur + c) : 1.f) * wt;
       }
     }
   }
@@ -622,22 +624,22 @@ extern "C" int evo_branch_norm(const evo_branch_norm_params* p, void* stream) {
 }
 
 extern "C" int evo_glu_act(const void* gate, const void* up, int64_t ld, void* out, int64_t ldo, int64_t rows, int F, int act,
-                           const float* group_w, int group, int n_groups, int dtype, void* stream) {
-  EVO_REQUIRE(gate && up && out && F > 0 && ldo >= F && (act == 0 || act == 1), "evo_glu_act: bad arguments");
-  EVO_REQUIRE(group_w == nullptr || (group > 0 && n_groups > 0), "evo_glu_act: bad groups");
+                           const float* group_w, int64_t ldw, int group, int n_groups, int tail_w, int dtype, void* stream) {
+  EVO_REQUIRE(gate && out && F > 0 && ldo >= F && act >= 0 && act <= 2, "evo_glu_act: bad arguments");
+  EVO_REQUIRE(group_w == nullptr || (group > 0 && n_groups > 0 && ldw >= n_groups + (tail_w ? 1 : 0)), "evo_glu_act: bad groups");
   if (rows == 0) return 0;
   const int av = dtype ? 16 : 8;
-  const bool vec = F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && (group_w == nullptr || group % 4 == 0) && aligned_to(gate, av) && aligned_to(up, av) && aligned_to(out, av);
+  const bool vec = F % 4 == 0 && ld % 4 == 0 && ldo % 4 == 0 && (group_w == nullptr || (group % 4 == 0)) && aligned_to(gate, av) && aligned_to(up, av) && aligned_to(out, av);
   const int per = 256 * (vec ? 4 : 1);
   EVO_REQUIRE((ldo + per - 1) / per <= 65535, "evo_glu_act: row too wide");
   dim3 grid((unsigned)rows, (unsigned)((ldo + per - 1) / per)), block(256);
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype) {
-    if (vec) glu_act_kernel<float, true><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, group, n_groups);
-    else glu_act_kernel<float, false><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, group, n_groups);
+    if (vec) glu_act_kernel<float, true><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, ldw, group, n_groups, tail_w);
+    else glu_act_kernel<float, false><<<grid, block, 0, st>>>((const float*)gate, (const float*)up, ld, (float*)out, ldo, F, act, group_w, ldw, group, n_groups, tail_w);
   } else {
-    if (vec) glu_act_kernel<bf16, true><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, group, n_groups);
-    else glu_act_kernel<bf16, false><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, group, n_groups);
+    if (vec) glu_act_kernel<bf16, true><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, ldw, group, n_groups, tail_w);
+    else glu_act_kernel<bf16, false><<<grid, block, 0, st>>>((const bf16*)gate, (const bf16*)up, ld, (bf16*)out, ldo, F, act, group_w, ldw, group, n_groups, tail_w);
   }
   return check_launch("evo_glu_act");
 }

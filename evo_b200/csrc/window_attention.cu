@@ -1,7 +1,8 @@
 // Softmax attention over a linear key/value cache with (a) a sliding window that also keeps the first tokens of the
 // sequence, (b) one or two score maps per head over the same values (differential attention: o = a1 - lambda * a2),
 // (c) an optional per-head RMS norm without weight, (d) an optional sigmoid output gate, (e) optionally soft-capped scores, a learned
-// sink in the softmax denominator and, before the window, one pooled key/value per block of tokens -- one fused kernel; the
+// sink in the softmax denominator, a per-head bias that grows with the logarithm of the distance and, before the window, one pooled
+// key/value per block of tokens -- one fused kernel; the
 // scores, the softmax weights, the combination of the maps and the head norm are fp32 whatever the activation type.
 //
 // Work per query is bounded by window + keep_first keys, so the kernel is a CUDA-core streaming-softmax kernel: one warp
@@ -66,6 +67,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // soft cap of a scaled score: cap * tanh(s / cap), off when cap <= 0
 __device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
+// what the distance between query and key takes off the score: r1 ln(1 + r2 (i - j)); r1 = 0 when the head has no such bias
+__device__ __forceinline__ float distance_bias(float r1, float r2, int64_t dist) { return r1 != 0.f ? r1 * logf(1.f + r2 * (float)dist) : 0.f; }
+__device__ __forceinline__ void distance_numbers(const evo_window_attn_params& p, int h, float& r1, float& r2) {
+  r1 = p.dist_r1 ? __bfloat162float(((const bf16*)p.dist_r1)[h]) : 0.f;
+  r2 = p.dist_r1 ? __bfloat162float(((const bf16*)p.dist_r2)[h]) : 0.f;
+}
 // pooled blocks that position i sees: those that end at or before i - window
 __device__ __forceinline__ int64_t blocks_seen(int64_t i, int64_t window, int64_t pool) {
   const int64_t n = i - window + 1;
@@ -87,13 +94,13 @@ struct Softmax {
 
 // scores of this lane's key for all maps -> running max / sum update; returns the lane's probabilities in pm
 template <int NM, int MAXCV>
-__device__ __forceinline__ bool tile_scores(Softmax<NM, MAXCV>& sm, const float* qrow, const float* krow, int dk, float scale, float cap, bool vis, float* pm) {
+__device__ __forceinline__ bool tile_scores(Softmax<NM, MAXCV>& sm, const float* qrow, const float* krow, int dk, float scale, float cap, float bias, bool vis, float* pm) {
   float s[NM];
 #pragma unroll
   for (int a = 0; a < NM; ++a) {
     float d = 0.f;
     for (int e = 0; e < dk; ++e) d = fmaf(qrow[a * dk + e], krow[a * dk + e], d);
-    s[a] = vis ? capped(d * scale, cap) : -INFINITY;
+    s[a] = vis ? capped(d * scale, cap) - bias : -INFINITY;
   }
   if (!__any_sync(0xffffffffu, vis)) return false;
 #pragma unroll
@@ -184,6 +191,8 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
   const T* pkb = pool_hi ? (const T*)p.pool_k + (int64_t)b * p.pool_batch_stride + (int64_t)g * kw : nullptr;
   const T* pvb = pool_hi ? (const T*)p.pool_v + (int64_t)b * p.pool_batch_stride + (int64_t)g * dv : nullptr;
 
+  float r1, r2;
+  distance_numbers(p, h, r1, r2);
   Softmax<NM, MAXCV> sm;
   sm.init();
   for (int part = 0; part < 3; ++part) {                  // kept first tokens, pooled blocks, window
@@ -207,7 +216,8 @@ __global__ void __launch_bounds__(QT * 32) window_attn_kernel(evo_window_attn_pa
       const int64_t kj = k0 + lane;
       const bool vis = lane < nk && (part == 1 ? kj < my_blocks : (kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first)));
       float pm[NM];
-      if (!tile_scores<NM, MAXCV>(sm, Qs + w * kw, Ks + (lane < nk ? lane : 0) * kst, dk, p.scale, p.softcap, vis, pm)) continue;
+      const float bias = (vis && part != 1) ? distance_bias(r1, r2, i - kj) : 0.f;       // pooled blocks have no distance
+      if (!tile_scores<NM, MAXCV>(sm, Qs + w * kw, Ks + (lane < nk ? lane : 0) * kst, dk, p.scale, p.softcap, bias, vis, pm)) continue;
       for (int r = 0; r < nk; ++r) {
         float pr[NM];
 #pragma unroll
@@ -254,6 +264,8 @@ __global__ void __launch_bounds__(QS_MAX * 32) window_attn_split_kernel(evo_wind
   const T* pkb = pool_hi ? (const T*)p.pool_k + (int64_t)b * p.pool_batch_stride + (int64_t)g * kw : nullptr;
   const T* pvb = pool_hi ? (const T*)p.pool_v + (int64_t)b * p.pool_batch_stride + (int64_t)g * dv : nullptr;
 
+  float r1, r2;
+  distance_numbers(p, h, r1, r2);
   Softmax<NM, MAXCV> sm;
   sm.init();
   for (int64_t t = w; t < n_keep + n_pool + n_win; t += nw) {
@@ -281,7 +293,7 @@ __global__ void __launch_bounds__(QS_MAX * 32) window_attn_split_kernel(evo_wind
       } else {
         for (int e = 0; e < dk; ++e) d = fmaf(Qs[a * dk + e], ldf(krow + a * dk + e), d);
       }
-      s[a] = vis ? capped(d * p.scale, p.softcap) : -INFINITY;
+      s[a] = vis ? capped(d * p.scale, p.softcap) - ((vis && !pooled) ? distance_bias(r1, r2, i - (k0 + lane)) : 0.f) : -INFINITY;
     }
 #pragma unroll
     for (int a = 0; a < NM; ++a) {
@@ -404,6 +416,7 @@ extern "C" int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream
   EVO_REQUIRE(p->dv <= 512, "evo_window_attn_fwd: dv (%d) must be <= 512", p->dv);
   EVO_REQUIRE(p->ldo >= (int64_t)p->H * p->dv, "evo_window_attn_fwd: ldo too small");
   EVO_REQUIRE(p->pool <= 0 || (p->window > 0 && p->pool_k && p->pool_v), "evo_window_attn_fwd: pooled blocks need a window and the pooled rows");
+  EVO_REQUIRE((p->dist_r1 == nullptr) == (p->dist_r2 == nullptr), "evo_window_attn_fwd: the distance bias needs both of its numbers");
   if (p->B == 0 || p->Lq == 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   static const char* env_mma = getenv("EVO_B200_WINDOW_ATTN_MMA");      // "0": always the CUDA-core kernel (comparisons)

@@ -10,7 +10,7 @@
 // Head sizes are padded to 16 in shared memory (zero columns); dk <= 128, dv <= 128 and dv % 8 == 0, otherwise the CUDA-core
 // kernel runs.  The tile walk is the CUDA-core kernel's: [0, keep_first), the pooled blocks that the CTA's last query sees, and the
 // union of the CTA's windows.  A soft cap is applied to the fp32 scores before the softmax (tanh from ex2 and a division), and a
-// sink enters the denominators at the end.
+// sink enters the denominators at the end; a distance bias is taken off the fp32 scores together with the mask.
 #include "common.cuh"
 #include "mma_sync.cuh"
 #include "../../include/evo_b200.h"
@@ -93,6 +93,9 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   const int64_t seen0 = windowed ? seen(i0) : 0, seen1 = windowed ? seen(i1) : 0, wseen_lo = windowed ? seen(wi_lo) : 0, wseen_hi = windowed ? seen(wi_hi) : 0;
   const bf16* pkb = pool_hi ? (const bf16*)p.pool_k + (int64_t)b * p.pool_batch_stride + (int64_t)g * NM * dk : nullptr;
   const bf16* pvb = pool_hi ? (const bf16*)p.pool_v + (int64_t)b * p.pool_batch_stride + (int64_t)g * dv : nullptr;
+  // distance bias r1 ln(1 + r2 d), in base-2 units: r1 log2(1 + r2 d)
+  const bool biased = p.dist_r1 != nullptr;
+  const float r1 = biased ? __bfloat162float(((const bf16*)p.dist_r1)[h]) : 0.f, r2 = biased ? __bfloat162float(((const bf16*)p.dist_r2)[h]) : 0.f;
 
   for (int part = 0; part < 3; ++part) {               // kept first tokens, pooled blocks, window
     const int64_t lo = part == 2 ? win_lo : 0, hi = part == 0 ? keep_hi : (part == 1 ? pool_hi : i_hi + 1);
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
       } else {
         if (t_lo > wi_hi) continue;
         if (windowed && wi_lo - t_hi >= p.window && t_lo >= p.keep_first) continue;
-        full = nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
+        full = !biased && nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
       }
 
 #pragma unroll
@@ -188,7 +191,8 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
             const bool vis = (n * 8 + qc + (c & 1)) < nk &&
                              (pooled ? kj < ((c < 2) ? seen0 : seen1) : (kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first)));
             const float sc = capped ? cap_out * (1.f - __fdividef(2.f, ex2(Pm[0][n][c] * cap_in) + 1.f)) : Pm[0][n][c] * scale2;
-            const float s = vis ? sc : -INFINITY;                          // base-2 exponent: exp(x) = 2^(x log2 e)
+            float s = vis ? sc : -INFINITY;                                // base-2 exponent: exp(x) = 2^(x log2 e)
+            if (biased && vis && !pooled) s -= r1 * log2f(1.f + r2 * (float)(i - kj));
             Pm[0][n][c] = s;
             if (c < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
           }

@@ -132,6 +132,13 @@ def _load_nelovik(model_dir: str, config: dict, device, dtype, **kwargs):
     return _load_flat(family, model_dir, config, device, dtype)
 
 
+def _load_gakupel(model_dir: str, config: dict, device, dtype, **kwargs):
+    def family():
+        from .gakupel import Gakupel, GakupelConfig
+        return Gakupel, GakupelConfig
+    return _load_flat(family, model_dir, config, device, dtype)
+
+
 def _load_stripedhyena(model_dir: str, config: dict, device, dtype, model_name: str = "evo-1-8k-base", **kwargs):
     if dtype not in (None, torch.bfloat16):
         raise NotImplementedError("StripedHyena runs in bfloat16 (fp32 poles and residues) only")
@@ -143,6 +150,7 @@ ARCHITECTURES = {
     "Zaverax": (_load_zaverax, (torch.bfloat16, torch.float32)),
     "Movalorn": (_load_movalorn, (torch.bfloat16, torch.float32)),
     "Nelovik": (_load_nelovik, (torch.bfloat16, torch.float32)),
+    "Gakupel": (_load_gakupel, (torch.bfloat16, torch.float32)),
     "StripedHyena": (_load_stripedhyena, (torch.bfloat16,)),
     "StripedHyenaModelForCausalLM": (_load_stripedhyena, (torch.bfloat16,)),
 }

@@ -253,31 +253,8 @@ class Movalorn(StreamDecoder):
         self._record("moe_route", float(M) * D * esz, lambda: check(lib.evo_moe_route(
             ptr(h), h.shape[1], ptr(w[f"l{i}.mlp.router"]), ptr(w[f"l{i}.mlp.correction"]), ptr(route), ptr(chosen), M, D,
             E, top, f.router_scale, self._dt, self._stream()), "evo_moe_route"))
-        counts = torch.zeros(2, E, dtype=torch.int32, device=dev)                      # row 0: counts, row 1: the scatter's cursors
-        check(lib.evo_moe_count(ptr(chosen), n, E, ptr(counts), self._stream()), "evo_moe_count")
-        cnt = counts[0].cpu()                                                           # the one host round trip of the layer
-        off = torch.zeros(E + 1, dtype=torch.int64)
-        off[1:] = torch.cumsum(cnt.to(torch.int64), 0)
-        offsets = off[:E].to(torch.int32).to(dev)
-        total = int(off[E])
-        perm = torch.empty(max(total, 1), dtype=torch.int32, device=dev)
-        slot_of = torch.empty(M, top, dtype=torch.int32, device=dev)
-        check(lib.evo_moe_scatter(ptr(chosen), n, top, E, ptr(offsets), C.c_void_p(counts.data_ptr() + 4 * E), ptr(perm), ptr(slot_of), self._stream()), "evo_moe_scatter")
-        Kp = h.shape[1]
-        hs = torch.empty(max(total, 1), Kp, dtype=self.act_dtype, device=dev)
-        self._record("moe_gather", 2.0 * total * Kp * esz, lambda: check(lib.evo_gather_rows(ptr(h), Kp * esz, ptr(hs), Kp * esz, ptr(perm), total, Kp * esz, self._stream()), "evo_gather_rows"))
-        up0, down0 = sp["experts"][0]
-        ys = torch.empty(max(total, 1), down0.Np, dtype=self.act_dtype, device=dev)
-        for e in range(E):
-            lo, ne = int(off[e]), int(cnt[e])
-            if ne == 0:
-                continue
-            up, down = sp["experts"][e]
-            z = self._linear(hs[lo:lo + ne], up, ne)
-            a = torch.empty(ne, down.Kp, dtype=self.act_dtype, device=dev)
-            self._record("glu_act", 3.0 * esz * ne * f.ff, lambda: check(lib.evo_glu_act(
-                ptr(z), C.c_void_p(z.data_ptr() + f.ff * esz), up.Np, ptr(a), down.Kp, ne, f.ff, 1, None, 0, 0, self._dt, self._stream()), "evo_glu_act"))
-            self._linear(a, down, ne, out=ys[lo:lo + ne])
+        ys, slot_of = self._run_chosen_experts(h, M, chosen, sp["experts"], f.ff, E, top)
+        down0 = sp["experts"][0][1]
         # the always-on expert and the branch gate read every row
         rest = sp["rest"]
         zr = self._linear(h, rest, M)
@@ -286,13 +263,13 @@ class Movalorn(StreamDecoder):
             sd = sp["shared_down"]
             a = torch.empty(M, sd.Kp, dtype=self.act_dtype, device=dev)
             self._record("glu_act", 3.0 * esz * M * f.shared_ff, lambda: check(lib.evo_glu_act(
-                ptr(zr), C.c_void_p(zr.data_ptr() + f.shared_ff * esz), rest.Np, ptr(a), sd.Kp, M, f.shared_ff, 1, None, 0, 0, self._dt, self._stream()), "evo_glu_act"))
+                ptr(zr), C.c_void_p(zr.data_ptr() + f.shared_ff * esz), rest.Np, ptr(a), sd.Kp, M, f.shared_ff, 1, None, 0, 0, 0, 0, self._dt, self._stream()), "evo_glu_act"))
             base = self._linear(a, sd, M)
             ldb = sd.Np
         ldo = _round_up(D, 64)
         y = torch.empty(M, ldo, dtype=self.act_dtype, device=dev)
         self._record("moe_combine", float(M) * D * esz * (2.0 + top), lambda: check(lib.evo_moe_combine(
-            ptr(ys), down0.Np, ptr(base), ldb, ptr(route), ptr(chosen), ptr(slot_of), ptr(y), ldo, M, D, E, top, self._dt, self._stream()), "evo_moe_combine"))
+            ptr(ys), down0.Np, ptr(base), ldb, ptr(route), E, 0, ptr(chosen), ptr(slot_of), ptr(y), ldo, M, D, E, top, self._dt, self._stream()), "evo_moe_combine"))
         return _Pending(y, ldo, zr.data_ptr() + 2 * f.shared_ff * esz, rest.Np, w[f"l{i}.rg2.b"], self._packed["gain"][f"l{i}.norm2b"], hold=zr)
 
     def _feed_forward(self, i, f, h, M, captured=False):
@@ -311,7 +288,7 @@ class Movalorn(StreamDecoder):
                 f.experts, f.top, f.router_scale, self._dt, self._stream()), "evo_moe_route"))
         self._record("glu_act", 3.0 * esz * M * F, lambda: check(lib.evo_glu_act(
             ptr(z), C.c_void_p(z.data_ptr() + F * esz), ld, ptr(a), pk["down"].Kp, M, F, 0 if f.kind == "dense" else 1,
-            ptr(route), f.ff if route is not None else 0, f.experts if route is not None else 0, self._dt, self._stream()), "evo_glu_act"))
+            ptr(route), f.experts if route is not None else 0, f.ff if route is not None else 0, f.experts if route is not None else 0, 0, self._dt, self._stream()), "evo_glu_act"))
         y = self._linear(a, pk["down"], M)
         return _Pending(y, pk["down"].Np, z.data_ptr() + 2 * F * esz, ld, w[f"l{i}.rg2.b"], self._packed["gain"][f"l{i}.norm2b"], hold=z)
 

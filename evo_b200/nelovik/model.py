@@ -22,7 +22,7 @@ from typing import Optional
 import torch
 
 from .. import _lib
-from .._lib import (ConvActParams, GatedDeltaParams, QkPrepParams, SsdParams, SumNormParams, WindowAttnParams, check, ptr)
+from .._lib import QkPrepParams, SsdParams, SumNormParams, WindowAttnParams, check, ptr
 from ..stream_model import StreamDecoder, _Packed, _round_up
 from .config import NelovikConfig
 
@@ -117,53 +117,9 @@ class Nelovik(StreamDecoder):
         nbytes = rows * cfg.width * (8.0 + esz * (len(branches) + len(outs)))
         self._record("sum_norm", nbytes, lambda: check(_lib.lib().evo_sum_norm(C.byref(p), self._stream()), "evo_sum_norm"))
 
-    def _conv(self, r, src_ptr, ld, weight, bias, channels, taps, B, L, rec, fresh):
-        """SiLU(short convolution) of `channels` columns starting at src_ptr -> (B*L, channels); the carried inputs live in rec.fir_state_dict[r]."""
-        dev = weight.device
-        out = torch.empty(B * L, channels, dtype=self.act_dtype, device=dev)
-        carry, zero = None, 1
-        if taps > 1:
-            carry = rec.fir_state_dict.get(r)
-            zero = 0
-            if carry is None or fresh:
-                if carry is None:
-                    carry = rec.fir_state_dict[r] = torch.empty(B, taps - 1, channels, dtype=torch.float32, device=dev)
-                zero = 1
-        cp = ConvActParams(inp=src_ptr, ld=ld, weight=weight.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
-                           carry=carry.data_ptr() if carry is not None else None, zero_start=zero, out=out.data_ptr(), ldo=channels,
-                           B=B, L=L, C=channels, taps=taps, act=1, dtype=self._dt)
-        self._record("conv_act", 2.0 * out.element_size() * B * L * channels, lambda: check(_lib.lib().evo_conv_act(C.byref(cp), self._stream()), "evo_conv_act"))
-        return out
-
-    def _matrix_state(self, r, rec, B, H, dk, dv, fresh):
-        state = rec.state_dict.get(r)
-        if state is None:
-            state = rec.state_dict[r] = torch.empty(B, H, dk, dv, dtype=torch.float32, device=self.device)
-            return state, 1
-        return state, 1 if fresh else 0
-
     def _delta(self, r, i, m, h, B, L, rec, fresh):
-        pk = self._packed["layers"][i]
-        M, dev = B * L, h.device
-        w = self.weights
-        z = self._linear(h, pk["in"], M)
-        esz, ldz = z.element_size(), pk["in"].Np
-        qk, vw = m.kv_heads * m.dim, m.heads * m.vdim
-        cw = 2 * qk + vw
-        c = self._conv(r, z.data_ptr(), ldz, pk["conv"], None, cw, m.taps, B, L, rec, fresh)
-        state, zero = self._matrix_state(r, rec, B, m.heads, m.dim, m.vdim, fresh)
-        ldo = _round_up(vw, 64)
-        out = torch.empty(M, ldo, dtype=self.act_dtype, device=dev)
-        p = f"l{i}.mix."
-        gp = GatedDeltaParams(q=c.data_ptr(), k=c.data_ptr() + qk * esz, v=c.data_ptr() + 2 * qk * esz, ld=cw,
-                              b=z.data_ptr() + (cw + vw) * esz, a=z.data_ptr() + (cw + vw + m.heads) * esz, gate=z.data_ptr() + cw * esz, ldz=ldz,
-                              A_log=w[p + "A_log"].data_ptr(), dt_bias=w[p + "dt_bias"].data_ptr(), norm_w=w[p + "norm"].data_ptr(),
-                              eps=self.config.eps, unit_eps=1e-6, q_scale=m.dim ** -0.5, state=state.data_ptr(), zero_start=zero,
-                              out=out.data_ptr(), ldo=ldo, dtype=self._dt, B=B, L=L, H=m.heads, G=m.kv_heads, dk=m.dim, dv=m.vdim)
-        nws = _lib.lib().evo_gated_delta_workspace(C.byref(gp))
-        ws = torch.empty(nws, dtype=torch.uint8, device=dev) if nws else None
-        self._record("gated_delta", 4.0 * M * m.heads * m.dim * m.vdim, lambda: check(_lib.lib().evo_gated_delta_fwd(C.byref(gp), ptr(ws), nws, self._stream()), "evo_gated_delta_fwd"))
-        return [(self._linear(out, pk["out"], M), pk["out"].Np, None, 1.0)]
+        y, ld = self._delta_mixer(r, i, m, h, B, L, rec, fresh)
+        return [(y, ld, None, 1.0)]
 
     def _ssd(self, r, i, s, z, col0, ldz, B, L, rec, fresh):
         """z columns [col0, ...) = [gate z | x B C | dt] of the shared projection -> the state-space mixer's output projection."""

@@ -23,7 +23,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from ._lib import EPI_NONE, check, ptr
+from ._lib import EPI_NONE, ConvActParams, GatedDeltaParams, check, ptr
 from .engine import KernelOps
 from .stripedhyena.cache import InferenceParams, RecurrentInferenceParams
 
@@ -160,6 +160,90 @@ class StreamDecoder(KernelOps, nn.Module):
         else:
             self._gemm(a, pk.w, out, M, pk.Np, pk.Kp, EPI_NONE, variant=2 if M <= 512 else self.gemm_variant)
         return out
+
+    # ---- mixers shared by several families ---------------------------------------------------------
+    def _conv(self, r, src_ptr, ld, weight, bias, channels, taps, B, L, rec, fresh):
+        """SiLU(short convolution) of `channels` columns starting at src_ptr -> (B*L, channels); the carried inputs live in rec.fir_state_dict[r]."""
+        dev = weight.device
+        out = torch.empty(B * L, channels, dtype=self.act_dtype, device=dev)
+        carry, zero = None, 1
+        if taps > 1:
+            carry = rec.fir_state_dict.get(r)
+            zero = 0
+            if carry is None or fresh:
+                if carry is None:
+                    carry = rec.fir_state_dict[r] = torch.empty(B, taps - 1, channels, dtype=torch.float32, device=dev)
+                zero = 1
+        cp = ConvActParams(inp=src_ptr, ld=ld, weight=weight.data_ptr(), bias=bias.data_ptr() if bias is not None else None,
+                           carry=carry.data_ptr() if carry is not None else None, zero_start=zero, out=out.data_ptr(), ldo=channels,
+                           B=B, L=L, C=channels, taps=taps, act=1, dtype=self._dt)
+        self._record("conv_act", 2.0 * out.element_size() * B * L * channels, lambda: check(_lib.lib().evo_conv_act(C.byref(cp), self._stream()), "evo_conv_act"))
+        return out
+
+    def _matrix_state(self, r, rec, B, H, dk, dv, fresh):
+        state = rec.state_dict.get(r)
+        if state is None:
+            state = rec.state_dict[r] = torch.empty(B, H, dk, dv, dtype=torch.float32, device=self.device)
+            return state, 1
+        return state, 1 if fresh else 0
+
+    def _delta_mixer(self, r, i, m, h, B, L, rec, fresh):
+        """Gated delta rule of layer i (tensors l<i>.mix.*; m: heads, kv_heads, dim, vdim, taps) on h (M, Kp) -> (output projection, its row stride)."""
+        pk = self._packed["layers"][i]
+        M, dev = B * L, h.device
+        w = self.weights
+        z = self._linear(h, pk["in"], M)
+        esz, ldz = z.element_size(), pk["in"].Np
+        qk, vw = m.kv_heads * m.dim, m.heads * m.vdim
+        cw = 2 * qk + vw
+        c = self._conv(r, z.data_ptr(), ldz, pk["conv"], None, cw, m.taps, B, L, rec, fresh)
+        state, zero = self._matrix_state(r, rec, B, m.heads, m.dim, m.vdim, fresh)
+        ldo = _round_up(vw, 64)
+        out = torch.empty(M, ldo, dtype=self.act_dtype, device=dev)
+        p = f"l{i}.mix."
+        gp = GatedDeltaParams(q=c.data_ptr(), k=c.data_ptr() + qk * esz, v=c.data_ptr() + 2 * qk * esz, ld=cw,
+                              b=z.data_ptr() + (cw + vw) * esz, a=z.data_ptr() + (cw + vw + m.heads) * esz, gate=z.data_ptr() + cw * esz, ldz=ldz,
+                              A_log=w[p + "A_log"].data_ptr(), dt_bias=w[p + "dt_bias"].data_ptr(), norm_w=w[p + "norm"].data_ptr(),
+                              eps=self.config.eps, unit_eps=1e-6, q_scale=m.dim ** -0.5, state=state.data_ptr(), zero_start=zero,
+                              out=out.data_ptr(), ldo=ldo, dtype=self._dt, B=B, L=L, H=m.heads, G=m.kv_heads, dk=m.dim, dv=m.vdim)
+        nws = _lib.lib().evo_gated_delta_workspace(C.byref(gp))
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev) if nws else None
+        self._record("gated_delta", 4.0 * M * m.heads * m.dim * m.vdim, lambda: check(_lib.lib().evo_gated_delta_fwd(C.byref(gp), ptr(ws), nws, self._stream()), "evo_gated_delta_fwd"))
+        return self._linear(out, pk["out"], M), pk["out"].Np
+
+    def _run_chosen_experts(self, h, M, chosen, experts, ff, E, top):
+        """Only the chosen experts of a mixture: the (token, choice) pairs of `chosen` (M, top) int32 are sorted by expert, and every
+        expert ([gate ; up] and down weights, packed, hidden size ff, SiLU-gated) runs on its slice of the gathered rows of h (M, Kp).
+        Returns (ys, slot_of): the experts' outputs in sorted order and the slot of every pair, for evo_moe_combine.  The per-expert
+        row counts come back to the host (one round trip), so this does not run inside a captured step."""
+        dev, lib = h.device, _lib.lib()
+        n, esz = M * top, h.element_size()
+        counts = torch.zeros(2, E, dtype=torch.int32, device=dev)                      # row 0: counts, row 1: the scatter's cursors
+        check(lib.evo_moe_count(ptr(chosen), n, E, ptr(counts), self._stream()), "evo_moe_count")
+        cnt = counts[0].cpu()                                                           # the one host round trip of the layer
+        off = torch.zeros(E + 1, dtype=torch.int64)
+        off[1:] = torch.cumsum(cnt.to(torch.int64), 0)
+        offsets = off[:E].to(torch.int32).to(dev)
+        total = int(off[E])
+        perm = torch.empty(max(total, 1), dtype=torch.int32, device=dev)
+        slot_of = torch.empty(M, top, dtype=torch.int32, device=dev)
+        check(lib.evo_moe_scatter(ptr(chosen), n, top, E, ptr(offsets), C.c_void_p(counts.data_ptr() + 4 * E), ptr(perm), ptr(slot_of), self._stream()), "evo_moe_scatter")
+        Kp = h.shape[1]
+        hs = torch.empty(max(total, 1), Kp, dtype=self.act_dtype, device=dev)
+        self._record("moe_gather", 2.0 * total * Kp * esz, lambda: check(lib.evo_gather_rows(ptr(h), Kp * esz, ptr(hs), Kp * esz, ptr(perm), total, Kp * esz, self._stream()), "evo_gather_rows"))
+        down0 = experts[0][1]
+        ys = torch.empty(max(total, 1), down0.Np, dtype=self.act_dtype, device=dev)
+        for e in range(E):
+            lo, ne = int(off[e]), int(cnt[e])
+            if ne == 0:
+                continue
+            up, down = experts[e]
+            z = self._linear(hs[lo:lo + ne], up, ne)
+            a = torch.empty(ne, down.Kp, dtype=self.act_dtype, device=dev)
+            self._record("glu_act", 3.0 * esz * ne * ff, lambda: check(lib.evo_glu_act(
+                ptr(z), C.c_void_p(z.data_ptr() + ff * esz), up.Np, ptr(a), down.Kp, ne, ff, 1, None, 0, 0, 0, 0, self._dt, self._stream()), "evo_glu_act"))
+            self._linear(a, down, ne, out=ys[lo:lo + ne])
+        return ys, slot_of
 
     # ---- forward ---------------------------------------------------------------------------------
     def forward(self, x, inference_params_dict=None, padding_mask=None, logits_rows=None):

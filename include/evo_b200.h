@@ -364,6 +364,9 @@ typedef struct {
   const void* sink;
   int64_t pool;
   const void* pool_k; const void* pool_v; int64_t pool_tok_stride, pool_batch_stride;
+  /*   dist_r1, dist_r2 (H, bf16; both or neither): a bias that grows with the distance is taken off the scaled (and capped) score of
+   *   key j for query i: score <- score - r1_h * ln(1 + r2_h * (i - j)). */
+  const void* dist_r1; const void* dist_r2;
 } evo_window_attn_params;
 int evo_window_attn_fwd(const evo_window_attn_params* p, void* stream);
 
@@ -401,10 +404,11 @@ typedef struct {
 } evo_branch_norm_params;
 int evo_branch_norm(const evo_branch_norm_params* p, void* stream);
 
-/* out[r, c] = act(gate[r, c]) * up[r, c] * w,  act 0 = tanh-form gelu, 1 = silu;  w = group_w[r, c / group] for c < n_groups * group
- * (fp32, rows x n_groups; NULL: 1) -- the weights of an expert mixture computed densely; columns [F, ldo) are zero. */
+/* out[r, c] = act(gate[r, c]) * up[r, c] * w,  act 0 = tanh-form gelu, 1 = silu, 2 = erf-form gelu;  up NULL: no second factor;
+ * w = group_w[r * ldw + c / group] for c < n_groups * group (fp32; NULL: 1) -- the weights of an expert mixture computed densely --
+ * and for the columns after the groups w = group_w[r * ldw + n_groups] if tail_w is set, else 1; columns [F, ldo) are zero. */
 int evo_glu_act(const void* gate, const void* up, int64_t ld, void* out, int64_t ldo, int64_t rows, int F, int act,
-                const float* group_w, int group, int n_groups, int dtype, void* stream);
+                const float* group_w, int64_t ldw, int group, int n_groups, int tail_w, int dtype, void* stream);
 /* out (rows, V) fp32 = in * mul */
 int evo_scale_logits(const void* in, int64_t ldi, float* out, int64_t rows, int V, float mul, int dtype, void* stream);
 
@@ -461,15 +465,29 @@ int evo_latent_attn_decode(const evo_latent_decode_params* p, void* workspace, s
  * weights (rows, E) fp32 = s * scale for the chosen experts, 0 for the others; chosen (rows, top) int32 (optional). */
 int evo_moe_route(const void* h, int64_t ldh, const void* router_w, const void* correction, float* weights, int32_t* chosen,
                   int64_t rows, int D, int E, int top, float scale, int dtype, void* stream);
+/* The router in general form.  logits = W . h in fp32 over E + n_extra rows of router_w (E experts, then n_extra further rows);
+ *   score_fn 0: s = softmax over the experts, 1: s = sigmoid per expert;   choice score c = s + correction;
+ *   groups > 1: the experts form `groups` equal runs of neighbours, a run's rank is the sum of its two largest c (of its one, when a run
+ *   has one expert), and only experts of the `keep` best runs can be chosen;   the `top` largest c are chosen (ties: lower index);
+ *   weights[r * ldw + e] = s_e * scale, or with normalize s_e / (sum of the chosen s + norm_eps) * scale; 0 for experts not chosen;
+ *   weights[r * ldw + E + x] = sigmoid(logit of extra row x)   (gates that ride along, e.g. of an always-on expert). */
+typedef struct {
+  const void* h; int64_t ldh; const void* router_w; const void* correction;
+  float* weights; int64_t ldw; int32_t* chosen;
+  int64_t rows; int D, E, top, n_extra;
+  int score_fn, groups, keep, normalize; float norm_eps, scale; int dtype;
+} evo_moe_route_params;
+int evo_moe_route_ex(const evo_moe_route_params* p, void* stream);
 /* Sparse execution of the chosen experts.  chosen (n = rows * top) int32:
  *   evo_moe_count    counts[e] += 1 per entry (counts zeroed by the caller);
  *   evo_moe_scatter  slot_of[i] = offsets[chosen[i]] + running cursor (cursor zeroed by the caller), perm[slot] = i / top;
  *   evo_gather_rows  dst row r = src row perm[r] (rows of width_bytes, all strides and bases multiples of 16 bytes);
- *   evo_moe_combine  out[t] = base[t] + sum_k weights[t, chosen[t,k]] * ys[slot_of[t,k]]  (fp32 sums, base optional, pad columns zero). */
+ *   evo_moe_combine  out[t] = g base[t] + sum_k weights[t*ldw + chosen[t,k]] * ys[slot_of[t,k]]  (fp32 sums, base optional, pad columns zero;
+ *                    g = weights[t*ldw + E] if base_w is set, else 1). */
 int evo_moe_count(const int32_t* chosen, int64_t n, int E, int32_t* counts, void* stream);
 int evo_moe_scatter(const int32_t* chosen, int64_t n, int top, int E, const int32_t* offsets, int32_t* cursor, int32_t* perm, int32_t* slot_of, void* stream);
 int evo_gather_rows(const void* src, int64_t ld_src_bytes, void* dst, int64_t ld_dst_bytes, const int32_t* perm, int64_t rows, int64_t width_bytes, void* stream);
-int evo_moe_combine(const void* ys, int64_t ldy, const void* base, int64_t ldb, const float* weights, const int32_t* chosen, const int32_t* slot_of,
+int evo_moe_combine(const void* ys, int64_t ldy, const void* base, int64_t ldb, const float* weights, int64_t ldw, int base_w, const int32_t* chosen, const int32_t* slot_of,
                     void* out, int64_t ldo, int64_t rows, int D, int E, int top, int dtype, void* stream);
 
 /* ==== designs whose layers run the mixer and the feed-forward side by side on two norms of the same stream, with matrix-state
@@ -548,7 +566,7 @@ typedef struct {
 } evo_ssd_params;
 int evo_ssd_fwd(const evo_ssd_params* p, void* stream);
 
-/* Preparation of attention projections whose query and key are normed over the WHOLE projection and partly rotated, one row at a time:
+/* Preparation of attention projections whose query and key are normed (over the WHOLE projection unless norm_per_head) and partly rotated, one row at a time:
  *   q <- rms(q + q_bias) * q_norm_w (over all H*dk entries), k likewise over G*dk, v <- v + v_bias;
  *   in every head the first rot_dims entries turn by pos * freq[i], entry i paired with entry i + rot_dims/2 (i < rot_dims/2; freq fp32);
  *   q is written back in place, [k | v] goes to the cache row of the token's position (pos = *pos_dev if given else pos0, plus its index). */
@@ -560,6 +578,12 @@ typedef struct {
   void* cache; int64_t cache_row, cache_batch_stride;
   int B; int64_t L; int H, G, dk, dv;
   int64_t pos0; const int64_t* pos_dev; int dtype;
+  /* optional extensions (off when zero):
+   *   norm_per_head: the norms run over each head's dk entries and q_norm_w / k_norm_w hold dk entries shared by all heads;
+   *   q_temp_every > 0: after norm and rotation the query is multiplied by 1 + q_temp_coef * ln(pos / q_temp_every + 1), with the
+   *   integer quotient of (pos + 1) -- a query temperature that grows with the position in steps of q_temp_every tokens. */
+  int norm_per_head;
+  float q_temp_coef; int64_t q_temp_every;
 } evo_qk_prep_params;
 int evo_qk_prep(const evo_qk_prep_params* p, void* stream);
 
@@ -567,6 +591,43 @@ int evo_qk_prep(const evo_qk_prep_params* p, void* stream);
  * [pos, pos + L)), pooled row b = mean of the block's rows as the cache holds them (fp32 sum), `width` entries per row. */
 int evo_pool_rows(const void* cache, int64_t cache_row, int64_t cache_batch_stride, void* pooled, int64_t pooled_row, int64_t pooled_batch_stride,
                   int B, int64_t L, int width, int64_t pool, int64_t pos0, const int64_t* pos_dev, int dtype, void* stream);
+
+/* ==== designs that norm the OUTPUT of every sublayer (layer norm with weight and bias) before it joins the fp32 stream, whose sublayers
+ * read the stream itself, and that hand on a learned mix of all earlier layers' results (Gakupel). ==== */
+
+/* One row kernel between two sublayers:
+ *   t = sum_b scale[b] * y[b]                      (n_in <= 2 sublayer outputs of the activation type, fp32 sum)
+ *   x <- x + ln(t; norm_w, norm_b)                 (skipped when n_in == 0;  ln(u) = (u - mean) / sqrt(var + eps) * w + b, biased variance)
+ *   mix_n > 0:  stack[mix_n - 1] <- x;  x <- sum_{j < mix_n} mix_w[j] * stack[j]      (stack (slots, rows, D) fp32, slot stride stack_stride)
+ *   out <- x, or ln(x; out_norm_w, out_norm_b) when out_norm_w is given, in the activation type, columns [D, ldo) zero
+ * x is read from x_in (default: x) and written to x; with `gather` (row indices) only those rows are read and nothing but `out` is written. */
+typedef struct {
+  float* x; const float* x_in;
+  const void* y[2]; int64_t ldy[2]; float scale[2]; int n_in;
+  const void* norm_w; const void* norm_b; float eps;
+  float* stack; int64_t stack_stride; int mix_n; const void* mix_w;
+  void* out; int64_t ldo; const void* out_norm_w; const void* out_norm_b;
+  int dtype; int64_t rows; int D; const int64_t* gather;
+} evo_post_norm_params;
+int evo_post_norm(const evo_post_norm_params* p, void* stream);
+
+/* Matrix memory with exponential gates kept stable by a running maximum (mLSTM), per head h over q, k (H*dk) and v (H*dv) of a row and
+ * the raw gate projections gi, gf (H):   i = cap tanh((gi + i_bias) / cap),  f = logsigmoid(cap tanh((gf + f_bias) / cap))   (cap <= 0: no cap)
+ *   m' = max(f + m, i);  S <- e^{f + m - m'} S + e^{i - m'} k v^T;  n likewise with k;  o = S^T (q q_scale) / (max(|n . q q_scale|, e^{-m'}) + den_eps)
+ *   out = o / sqrt(mean_c o^2 + eps) * norm_w[h*dv + c] * sigmoid(gate[h*dv + c])
+ * state (B, H, dk, dv + 1) fp32: S with n as its last column; mstate (B, H) fp32: m (zero_start: both start at 0).
+ * workspace: evo_mlstm_workspace() bytes (0 unless a head's value channels are spread over several CTAs). */
+typedef struct {
+  const void* q; const void* k; const void* v; int64_t ld;
+  const void* gi; const void* gf; int64_t ldg;
+  const void* i_bias; const void* f_bias; float cap, q_scale, den_eps;
+  const void* gate; int64_t ld_gate; const void* norm_w; float eps;
+  float* state; float* mstate; int zero_start;
+  void* out; int64_t ldo; int dtype;
+  int B; int64_t L; int H, dk, dv;
+} evo_mlstm_params;
+size_t evo_mlstm_workspace(const evo_mlstm_params* p);
+int evo_mlstm_fwd(const evo_mlstm_params* p, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

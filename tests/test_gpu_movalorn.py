@@ -124,14 +124,14 @@ def test_glu_activation_with_group_weights_and_scaled_logits(act):
     wts[0, 1] = 0.0
     zd, wd, out = z.to(DEV), wts.to(DEV), torch.full((M, F + 12), 3.0, device=DEV)
     lib = _lib.lib()
-    check(lib.evo_glu_act(ptr(zd), C.c_void_p(zd.data_ptr() + 4 * F), 2 * F + 3, ptr(out), F + 12, M, F, act, ptr(wd), grp, E, 1, _stream()))
+    check(lib.evo_glu_act(ptr(zd), C.c_void_p(zd.data_ptr() + 4 * F), 2 * F + 3, ptr(out), F + 12, M, F, act, ptr(wd), E, grp, E, 0, 1, _stream()))
     fn = O.gelu_tanh if act == 0 else O.silu
     want = fn(z[:, :F].double()) * z[:, F:2 * F].double()
     for e in range(E):
         want[:, e * grp:(e + 1) * grp] *= wts[:, e:e + 1].double()
     _close(out[:, :F], want, 2e-6, "glu")
     assert (out[:, F:] == 0).all()
-    check(lib.evo_glu_act(ptr(zd), C.c_void_p(zd.data_ptr() + 4 * F), 2 * F + 3, ptr(out), F + 12, M, F, act, None, 0, 0, 1, _stream()))
+    check(lib.evo_glu_act(ptr(zd), C.c_void_p(zd.data_ptr() + 4 * F), 2 * F + 3, ptr(out), F + 12, M, F, act, None, 0, 0, 0, 0, 1, _stream()))
     _close(out[:, :F], fn(z[:, :F].double()) * z[:, F:2 * F].double(), 2e-6, "glu without weights")
     scaled = torch.empty(M, F, device=DEV)
     check(lib.evo_scale_logits(ptr(zd), 2 * F + 3, ptr(scaled), M, F, 0.37, 1, _stream()))
