@@ -218,7 +218,7 @@ MIXERS = {"attention": attention, "delta": gated_delta, "parallel": parallel_mix
 
 
 def forward(tokens: List[int], W: Dict[str, torch.Tensor], cfg: dict, dtype=torch.float64, taps: Optional[list] = None):
-    """Logits (T, V) of a whole sequence.  taps: receives every layer's result X_{i+1} (before the depth average)."""
+    """Logits (T, V) of a whole sequence.  taps: receives the stream every layer hands on (after the mix of the results so far)."""
     W = {k: v.to(dtype) for k, v in W.items()}
     eps = float(cfg["norm"]["eps"])
     x = W["embed"][torch.tensor(tokens)]
@@ -233,19 +233,96 @@ def forward(tokens: List[int], W: Dict[str, torch.Tensor], cfg: dict, dtype=torc
             y = dense_ff(x, sub(p + "mlp.")) if f.get("kind", "dense") == "dense" else moe_ff(x, sub(p + "mlp."), f)
             x = x + layer_norm(y, W[p + "norm2"], W[p + "norm2.b"], eps)
         results.append(x)
-        if taps is not None:
-            taps.append(x)
         a = W[p + "dwa"]
         x = sum(a[j] * results[j] for j in range(len(results)))
+        if taps is not None:
+            taps.append(x)
     x = layer_norm(x, W["final.norm"], W["final.norm.b"], eps)
     return x @ W["head"].T
 
 
-def random_weights(cfg: dict, shapes: Dict[str, tuple], seed: int = 0) -> Dict[str, torch.Tensor]:
-    """Random bf16-representable weights of a usable scale for the tensor table `shapes` (name -> shape)."""
+def make_config(layers=("parallel", "attention", "delta"), mlps=("dense", "moe", "moe"), width=64, vocab=97, ff=96, eps=1e-5,
+                att_heads=4, att_kv_heads=2, att_dim=16, rot_dims=8, rot_base=1000.0, att_scale=0.3,
+                left_heads=4, left_kv_heads=2, left_dim=16, left_vdim=12, left_scale_qk=0.25, temp_coef=0.4, temp_every=8, left_scale=1.3, right_scale=0.6,
+                mem_heads=2, mem_dim=12, mem_vdim=20, gate_cap=6.0,
+                heads=4, kv_heads=2, dim=8, vdim=16, taps=3,
+                experts=8, top=3, groups=4, keep=2, router_scale=1.5, expert_ff=24, shared_ff=40) -> dict:
+    """A small configuration in the checkpoints' own keys; every layer of a kind gets the same sizes (tests change single entries)."""
+    out = []
+    for kind, mlp in zip(layers, mlps):
+        if kind == "attention":
+            m = {"heads": att_heads, "kv_heads": att_kv_heads, "dim": att_dim, "vdim": att_dim, "scale": att_scale}
+            if rot_dims:
+                m["rot"] = {"base": rot_base, "dims": rot_dims}
+        elif kind == "delta":
+            m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": taps}
+        else:
+            left = {"heads": left_heads, "kv_heads": left_kv_heads, "dim": left_dim, "vdim": left_vdim, "scale": left_scale_qk}
+            if temp_every:
+                left["q_temp"] = {"coef": temp_coef, "every": temp_every}
+            m = {"left": left, "left_scale": left_scale, "right": {"heads": mem_heads, "dim": mem_dim, "vdim": mem_vdim, "gate_cap": gate_cap}, "right_scale": right_scale}
+        if mlp == "dense":
+            f = {"kind": "dense", "ff": ff}
+        elif mlp == "moe":
+            router = {"experts": experts, "top": top, "scale": router_scale}
+            if groups:
+                router["groups"] = {"count": groups, "keep": keep}
+            f = {"kind": "moe", "expert": {"ff": expert_ff}, "router": router}
+            if shared_ff:
+                f["shared"] = {"ff": shared_ff}
+        else:
+            f = None
+        out.append({"type": kind, "mixer": m, "mlp": f})
+    return {"architecture": "Gakupel", "layers": out, "norm": {"eps": eps}, "vocab": vocab, "width": width}
+
+
+def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
+    """Checkpoint tensor name -> shape for a configuration."""
+    d, V = cfg["width"], cfg["vocab"]
+    out = {"embed": (V, d)}
+    for i, layer in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        out[p + "norm1"] = out[p + "norm1.b"] = (d,)
+        q = p + "mix."
+        if layer["type"] == "attention":
+            H, G, dk = m["heads"], m["kv_heads"], m["dim"]
+            out.update({q + "q": (H * dk, d), q + "k": (G * dk, d), q + "q.norm": (dk,), q + "k.norm": (dk,), q + "o": (d, H * dk)})
+        elif layer["type"] == "delta":
+            H, G, dk, dv, t = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+            out.update({q + "q": (G * dk, d), q + "q.conv": (G * dk, t), q + "k": (G * dk, d), q + "k.conv": (G * dk, t), q + "v": (H * dv, d), q + "v.conv": (H * dv, t),
+                        q + "b": (H, d), q + "a": (H, d), q + "A_log": (H,), q + "dt_bias": (H,), q + "norm": (dv,), q + "g": (H * dv, d), q + "o": (d, H * dv)})
+        else:
+            a, s = m["left"], m["right"]
+            H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            out.update({q + "left.q": (H * dk, d), q + "left.k": (G * dk, d), q + "left.v": (G * dv, d), q + "left.q.norm": (H * dk,), q + "left.k.norm": (G * dk,),
+                        q + "left.r1": (H,), q + "left.r2": (H,), q + "left.o": (d, H * dv)})
+            H, dk, dv = s["heads"], s["dim"], s["vdim"]
+            out.update({q + "right.q": (H * dk, d), q + "right.k": (H * dk, d), q + "right.v": (H * dv, d), q + "right.g": (H * dv, d), q + "right.o": (d, H * dv),
+                        q + "right.norm": (H * dv,), q + "right.i": (H, d), q + "right.i.b": (H,), q + "right.f": (H, d), q + "right.f.b": (H,)})
+        f = layer.get("mlp")
+        if f is not None:
+            out[p + "norm2"] = out[p + "norm2.b"] = (d,)
+            if f.get("kind", "dense") == "dense":
+                out.update({p + "mlp.up": (f["ff"], d), p + "mlp.down": (d, f["ff"])})
+            else:
+                e = f["expert"]["ff"]
+                for k in range(f["router"]["experts"]):
+                    out.update({f"{p}mlp.e{k}.gate": (e, d), f"{p}mlp.e{k}.up": (e, d), f"{p}mlp.e{k}.down": (d, e)})
+                out.update({p + "mlp.router": (f["router"]["experts"], d), p + "mlp.correction": (f["router"]["experts"],)})
+                if f.get("shared"):
+                    e = f["shared"]["ff"]
+                    out.update({p + "mlp.shared.gate": (e, d), p + "mlp.shared.up": (e, d), p + "mlp.shared.down": (d, e), p + "mlp.shared.sg": (1, d)})
+        out[p + "dwa"] = (i + 2,)
+    out["final.norm"] = out["final.norm.b"] = (d,)
+    out["head"] = (V, d)
+    return out
+
+
+def random_weights(cfg: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random bf16-representable weights of a usable scale."""
     g = torch.Generator().manual_seed(seed)
     out = {}
-    for name, shape in shapes.items():
+    for name, shape in tensor_shapes(cfg).items():
         leaf = name.split(".")[-1]
         if leaf in ("norm1", "norm2") or name == "final.norm" or name.endswith((".q.norm", ".k.norm", "mix.norm", "right.norm")):
             v = 1.0 + torch.randn(shape, generator=g) * 0.1
@@ -272,5 +349,5 @@ def random_weights(cfg: dict, shapes: Dict[str, tuple], seed: int = 0) -> Dict[s
             v = torch.randn(shape, generator=g)
         else:
             v = torch.randn(shape, generator=g) / math.sqrt(shape[-1])
-        out[name] = v.to(torch.bfloat16).to(torch.float32)
+        out[name] = v.to(torch.bfloat16)
     return out
