@@ -1,6 +1,6 @@
 """bench.py — nucleotides/sec of the Evo-1 7B forward on B200 (BASELINE.json metric).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 8k|131k|1k|32k|gen|zaverax|movalorn] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload 8k|131k|1k|32k|gen|zaverax|movalorn|nelovik|gakupel] [--impl ours|reference]
 
 Workload "8k" (default, BASELINE.json configs[1]): evo-1-8k-base scoring forward, batch 8 x
 8192 nt of synthetic uniform ACGT (+BOS => L = 8193), bf16, random-init weights of the 7B
@@ -12,7 +12,8 @@ N > 1 (torchrun, one rank per GPU): independent replicas of the workload, no dat
 collective (weak scaling); "131k" runs the sequence-parallel forward instead.
 Workload "zaverax" (an option; the default workload and its JSON contract are unchanged): the Zaverax design beside StripedHyena at
 equal layer sizes, prefill and decode, with a per-kernel roofline breakdown (bench_arch).  Workload "movalorn": the same for the
-Movalorn design beside Zaverax, the closest family.  Workload "nelovik": the Nelovik design beside Zaverax likewise.
+Movalorn design beside Zaverax, the closest family.  Workload "nelovik": the Nelovik design beside Zaverax likewise.  Workload "gakupel":
+the Gakupel design beside Nelovik.
 --impl reference: the reference's own CPU implementation of the path.  stripedhyena==0.2.2 is
 not installable offline, so this arm times the oracle restatement (kind "port") on the host
 cores, rank 0 only, on a bounded sample of the same workload.
@@ -657,6 +658,31 @@ def _nelovik_models(size, dev):
     return nv, zv
 
 
+def _gakupel_models(size, dev):
+    """A Gakupel model and a Nelovik model (the closest family: fp32 stream, gated-delta layers, attention beside a matrix-state
+    recurrence) of equal width, depth, head count and dense feed-forward width, random weights.  Gakupel: a gated-delta layer (heads of
+    128 x 128, 4 taps), a parallel layer (biased sink attention with heads of 128 / 128 and a fourth as many key heads, beside a matrix
+    memory with heads of 128 x 128), a key-valued attention layer (heads of 128, 64 rotated entries) and another gated-delta layer; two
+    dense feed-forwards and two with 16 experts in 4 groups (4 chosen from 2 groups, one shared) whose chosen hidden width equals the
+    dense one.  Its attention is causal over the whole prompt, Nelovik's sees a window of 1024 tokens plus pooled blocks."""
+    from evo_b200.gakupel import Gakupel, GakupelConfig
+    nv, _ = _nelovik_models(size, dev)
+    s = ARCH_SIZES[size]
+    d, H = s["width"], s["heads"]
+    ff = (8 * d // 3 + 255) // 256 * 256
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": ff // 4}}
+    delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": H, "dim": 128, "vdim": 128, "conv": 4}}
+    par = {"type": "parallel", "mixer": {
+        "left": {"heads": H, "kv_heads": H // 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.25, "every": 512}}, "left_scale": 1.0,
+        "right": {"heads": H, "dim": 128, "vdim": 128, "gate_cap": 15.0}, "right_scale": 1.0}}
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": H // 2, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 10000.0}}}
+    gc = {"architecture": "Gakupel", "vocab": 512, "width": d, "norm": {"eps": 1e-5},
+          "layers": [dict(delta, mlp=dense), dict(par, mlp=moe), dict(att, mlp=dense), dict(delta, mlp=moe)]}
+    gk = Gakupel(GakupelConfig.from_dict(gc)).init_random(0, device=dev)
+    return gk, nv
+
+
 def bench_arch(args):
     """--workload zaverax: prefill and decode throughput of the Zaverax design beside StripedHyena at equal layer sizes (random
     weights, 4 layers each, one of them attention), with a per-kernel breakdown against the measured rooflines.  Inputs are larger
@@ -670,16 +696,16 @@ def bench_arch(args):
     fp32_lane_ops = 148 * 128 * peaks.get("sm_max_mhz", 1965.0) * 1e6        # CUDA-core fp32 instructions (lanes) per second at the maximum clock
     bound = {"gemm": ("flop/s", peaks["bf16_tflops"] * 1e12), "gemm_simt": ("flop/s", 2 * fp32_lane_ops), "attn": ("flop/s", peaks["bf16_tflops"] * 1e12),
              "window_attn": ("flop/s", peaks["bf16_tflops"] * 1e12), "hgrn2": ("fp32 lane-op/s", fp32_lane_ops),
-             "gated_delta": ("fp32 lane-op/s", fp32_lane_ops), "ssd": ("fp32 lane-op/s", fp32_lane_ops)}
+             "gated_delta": ("fp32 lane-op/s", fp32_lane_ops), "ssd": ("fp32 lane-op/s", fp32_lane_ops), "mlstm": ("fp32 lane-op/s", fp32_lane_ops)}
     family = args.workload
-    other = {"zaverax": "stripedhyena", "movalorn": "zaverax", "nelovik": "zaverax"}[family]
+    other = {"zaverax": "stripedhyena", "movalorn": "zaverax", "nelovik": "zaverax", "gakupel": "nelovik"}[family]
     bound.update({"mingru": ("B/s", peaks["hbm_gbs"] * 1e9), "latent_decode": ("B/s", peaks["hbm_gbs"] * 1e9)})
     out = {"workload": family, "metric": f"tokens/sec, prefill and decode, {family} beside {other} at equal sizes", "unit": "tok/s", "dtype": "bf16",
            "data": "synthetic", "steps": steps, "warmup": warmup, "peaks": peaks, "sizes": {}}
     launches = 0
     with ClockSampler(0) as clocks:
         for size, s in ARCH_SIZES.items():
-            zv, sh = {"zaverax": _arch_models, "movalorn": _movalorn_models, "nelovik": _nelovik_models}[family](size, dev)
+            zv, sh = {"zaverax": _arch_models, "movalorn": _movalorn_models, "nelovik": _nelovik_models, "gakupel": _gakupel_models}[family](size, dev)
             rec = {}
             for name, model in ((family, zv), (other, sh)):
                 B, L = s["prefill"]
@@ -754,14 +780,14 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS) + ["zaverax", "movalorn", "nelovik"])
+    ap.add_argument("--workload", default="8k", choices=list(WORKLOADS) + ["zaverax", "movalorn", "nelovik", "gakupel"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sub", action="store_true", help="default workload only: skip the sp131k / gen sub-records")
     ap.add_argument("--no-gen", action="store_true", help="skip the cached-generation sub-record")
     ap.add_argument("--sub-steps", type=int, default=3, help="timed steps of the 131k sub-record")
     ap.add_argument("--gen-tokens", type=int, default=None, help="new tokens of the end-to-end generate() run (default: 4096 = BASELINE configs[3])")
     args = ap.parse_args()
-    if args.workload in ("zaverax", "movalorn", "nelovik"):
+    if args.workload in ("zaverax", "movalorn", "nelovik", "gakupel"):
         return bench_arch(args)
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":

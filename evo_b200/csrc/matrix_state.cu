@@ -17,8 +17,11 @@
 // The delta rule needs S^T k before it can write: both products are taken from the decayed state in one pass,
 //   p = (gS)^T k,  r = (gS)^T q,  u = beta (v - p),  o = r + u (k . q),
 // and the rank-one update follows with u -- one shuffle fold per token instead of two.
-// The matrix memory's normaliser n is one more column of its state (a value channel that is always 1), so n.q falls out of the same loop;
-// its running maximum is a scalar scan over the round's tokens that one thread does between staging and the time loop.
+// The matrix memory's running maximum is a (max, +) scan over the round's tokens that one warp does between staging and the time loop.
+// Its normaliser n (a vector per head) never enters the time loop: within a round n_t.q_t = P_t (n_0.q_t) + sum_{s<=t} (prod_{s<r<=t} a_r) b_s (k_s.q_t)
+// with a, b the round's decay and input factors and P_t = a_0 .. a_t, so the warps take the round's k_s.q_t and n_0.q_t dot products from
+// the staged rows (one thread per pair), one thread per token folds them, and n_0 is advanced to the round's end the same way; every CTA of a head does this
+// for itself, so a head spread over several CTAs needs no exchange.
 // The single-token step is the same kernel with L == 1.
 #include "common.cuh"
 #include "../../include/evo_b200.h"
@@ -58,8 +61,9 @@ struct ScanArgs {
   // ssd output, or the un-normed read-outs of the other two when a head is spread over several CTAs: (rows, H*dv) fp32
   float* y;
   int B; int64_t L; int H, G, dk, dv;
-  // matrix memory: dv counts the normaliser's column (dv_real value channels + 1); gate biases, soft cap, e^{-m} per (row, head) beside y
-  int dv_real; const void* i_bias; const void* f_bias; float cap, den_eps; float* mstate; float* em;
+  // matrix memory: gate biases, soft cap, running maximum (B, H), and beside y the reciprocal denominators per (row, head);
+  // a head's state is its dk x dv matrix followed by the dk entries of the normaliser
+  const void* i_bias; const void* f_bias; float cap, den_eps; float* mstate; float* em;
 };
 
 // soft cap c tanh(z / c) (c <= 0: none) and log sigmoid
@@ -74,15 +78,20 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
   float2* kq = reinterpret_cast<float2*>(smem);            // [TCH][dkp]   (key, query) per state row
   float* vs = smem + 2 * TCH * dkp;                        // [TCH][dvp]
   float* sc = vs + TCH * dvp;                              // [TCH][4]     delta: (g, beta, k.q, -)   ssd: (a, D, -, -)
-  float* os = sc + TCH * 4;                                // [TCH][dvp]   delta read-outs
+  float* os = sc + TCH * 4;                                // [TCH][dvp]   delta / matrix-memory read-outs
+  float* nvec = os + TCH * dvp;                            // [dkp]        matrix memory: the normaliser at the round's start
+  float* kqd = nvec + dkp;                                 // [TCH][TCH]   k_s . q_t (s <= t)
+  float* n0q = kqd + TCH * TCH;                            // [TCH]        n_0 . q_t
   const int h = blockIdx.x, b = blockIdx.y, g = h / (p.H / p.G);
   const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nw = nthr >> 5;
   const int j0 = blockIdx.z * dvp;                         // first value channel of this CTA
   const int jl = (tid / LPC) * CPT, l = tid % LPC, j = j0 + jl;      // first of the thread's columns, within the CTA and within the head
   const T* kp = (const T*)p.kk + (int64_t)g * dk;
   const T* qp = (const T*)p.qq + (int64_t)g * dk;
-  const T* vp = (const T*)p.vv + (int64_t)h * (MODE == MODE_MLSTM ? p.dv_real : dv);
-  float* Sg = p.state ? p.state + ((int64_t)b * p.H + h) * dk * (int64_t)dv : nullptr;
+  const T* vp = (const T*)p.vv + (int64_t)h * dv;
+  float* Sg = p.state ? p.state + ((int64_t)b * p.H + h) * dk * (int64_t)(MODE == MODE_MLSTM ? dv + 1 : dv) : nullptr;
+  if (MODE == MODE_MLSTM)
+    for (int e = tid; e < dkp; e += nthr) nvec[e] = (Sg && !p.zero_start && e < dk) ? Sg[(int64_t)dk * dv + e] : 0.f;
   const float A = MODE == MODE_MLSTM ? 0.f : expf(__bfloat162float(((const bf16*)p.A_log)[h]));
   const float dtb = MODE == MODE_MLSTM ? 0.f : __bfloat162float(((const bf16*)p.dt_bias)[h]);
   float mrun = (MODE == MODE_MLSTM && p.mstate && !p.zero_start) ? p.mstate[(int64_t)b * p.H + h] : 0.f;      // thread 0's: the running maximum
@@ -144,26 +153,66 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
         }
         if (lane == 0) { sc[tt * 4 + 0] = expf(-A * dt); sc[tt * 4 + 1] = Dh; }
       }
-      if (MODE == MODE_MLSTM) {
-        for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = j0 + c < p.dv_real ? ldf(vp + row * p.ld + j0 + c) : (j0 + c == p.dv_real ? 1.f : 0.f);
-      } else {
-        for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = j0 + c < dv ? ldf(vp + row * p.ld + j0 + c) : 0.f;
-      }
+      for (int c = lane; c < dvp; c += 32) vs[tt * dvp + c] = j0 + c < dv ? ldf(vp + row * p.ld + j0 + c) : 0.f;
     }
     __syncthreads();
     if (MODE == MODE_MLSTM) {
-      if (tid == 0) {
-        for (int tt = 0; tt < nt; ++tt) {
-          const float f = sc[tt * 4 + 0], i = sc[tt * 4 + 1];
-          const float mn = fmaxf(f + mrun, i);
-          sc[tt * 4 + 0] = expf(f + mrun - mn);
-          sc[tt * 4 + 1] = expf(i - mn);
-          sc[tt * 4 + 2] = expf(-mn);
-          if (p.em && blockIdx.z == 0) p.em[(row0 + tt) * p.H + h] = sc[tt * 4 + 2];
-          mrun = mn;
+      if (warp == 0) {
+        // m_t = max(f_t + m_{t-1}, i_t) over the round as two prefix scans: with F_t = f_0 + .. + f_t,  m_t = F_t + max(m_start, max_{s<=t} (i_s - F_s))
+        const bool on = lane < nt;
+        const float f = on ? sc[lane * 4 + 0] : 0.f, i = on ? sc[lane * 4 + 1] : -INFINITY;
+        float F = f;
+#pragma unroll
+        for (int o = 1; o < TCH; o <<= 1) { const float u = __shfl_up_sync(0xffffffffu, F, o); if (lane >= o) F += u; }
+        float g = i - F;
+#pragma unroll
+        for (int o = 1; o < TCH; o <<= 1) { const float u = __shfl_up_sync(0xffffffffu, g, o); if (lane >= o) g = fmaxf(g, u); }
+        const float m = F + fmaxf(mrun, g);
+        float mprev = __shfl_up_sync(0xffffffffu, m, 1);
+        if (lane == 0) mprev = mrun;
+        if (on) { sc[lane * 4 + 0] = expf(f + mprev - m); sc[lane * 4 + 1] = expf(i - m); sc[lane * 4 + 2] = expf(-m); }
+        mrun = __shfl_sync(0xffffffffu, m, nt - 1);
+      }
+      // the round's dot products, one thread each: pair (s, t), s <= t, has index t (t + 1) / 2 + s; after the pairs, n_0 . q_t.  Two state rows
+      // (k, q, k, q) per 16-byte read; neighbouring threads hold neighbouring s (or, for n_0, t) and start that many reads into the row, so
+      // that the threads of a quarter warp read different banks
+      const int npair = nt * (nt + 1) / 2, nq4 = dkp / 2;
+      for (int task = tid; task < npair + nt; task += nthr) {
+        int t = task - npair, s_ = nt;
+        if (task < npair) { t = 0; while ((t + 1) * (t + 2) / 2 <= task) ++t; s_ = task - t * (t + 1) / 2; }
+        const float4* qt = reinterpret_cast<const float4*>(kq + t * dkp);
+        float d0 = 0.f, d1 = 0.f;
+        const int msk = nq4 - 1;                          // dkp is a power of two
+        if (s_ < nt) {
+          const float4* ks = reinterpret_cast<const float4*>(kq + s_ * dkp);
+#pragma unroll 8
+          for (int i = 0; i < nq4; ++i) { const int e = (s_ + i) & msk; const float4 a = ks[e], c = qt[e]; d0 = fmaf(a.x, c.y, d0); d1 = fmaf(a.z, c.w, d1); }
+          kqd[s_ * TCH + t] = d0 + d1;
+        } else {
+          const float2* nv2 = reinterpret_cast<const float2*>(nvec);
+#pragma unroll 8
+          for (int i = 0; i < nq4; ++i) { const int e = (t + i) & msk; const float4 c = qt[e]; const float2 n2 = nv2[e]; d0 = fmaf(n2.x, c.y, d0); d1 = fmaf(n2.y, c.w, d1); }
+          n0q[t] = d0 + d1;
         }
       }
       __syncthreads();
+      // one thread per token folds its row of products into n_t . q_t and keeps the reciprocal denominator; the normaliser moves to the round's end
+      if (tid < nt) {                                      // n_t . q_t = (..((n_0.q_t) a_0 + b_0 k_0.q_t) a_1 + ..) a_t + b_t k_t.q_t
+        float acc = n0q[tid];
+#pragma unroll
+        for (int s_ = 0; s_ < TCH; ++s_)
+          if (s_ <= tid) acc = fmaf(acc, sc[s_ * 4 + 0], sc[s_ * 4 + 1] * kqd[s_ * TCH + tid]);
+        const float inv = 1.f / (fmaxf(fabsf(acc), sc[tid * 4 + 2]) + p.den_eps);
+        sc[tid * 4 + 3] = inv;
+        if (p.em && blockIdx.z == 0) p.em[(row0 + tid) * p.H + h] = inv;
+      }
+      for (int e = tid; e < dkp; e += nthr) {
+        float n = nvec[e];
+#pragma unroll
+        for (int s_ = 0; s_ < TCH; ++s_)
+          if (s_ < nt) n = fmaf(n, sc[s_ * 4 + 0], sc[s_ * 4 + 1] * kq[s_ * dkp + e].x);
+        nvec[e] = n;
+      }
     }
     // ---- time loop
     for (int tt = 0; tt < nt; ++tt) {
@@ -252,21 +301,20 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
     if (MODE == MODE_MLSTM && !p.y) {
       __syncthreads();
       // normaliser, head norm, weight over all heads, sigmoid gate, store: one warp per token
-      const bf16* nwt = (const bf16*)p.norm_w + (int64_t)h * p.dv_real;
-      const int dvr = p.dv_real;
+      const bf16* nwt = (const bf16*)p.norm_w + (int64_t)h * dv;
       for (int tt = warp; tt < nt; tt += nw) {
         const int64_t row = row0 + tt;
-        const float inv = 1.f / (fmaxf(fabsf(os[tt * dvp + dvr]), sc[tt * 4 + 2]) + p.den_eps);
+        const float inv = sc[tt * 4 + 3];
         float ss = 0.f;
-        for (int c = lane; c < dvr; c += 32) { const float o = os[tt * dvp + c] * inv; ss = fmaf(o, o, ss); }
+        for (int c = lane; c < dv; c += 32) { const float o = os[tt * dvp + c] * inv; ss = fmaf(o, o, ss); }
         ss = warp_sum(ss);
-        const float rstd = inv / sqrtf(ss / (float)dvr + p.eps);
+        const float rstd = inv / sqrtf(ss / (float)dv + p.eps);
         T* orow = (T*)p.out + row * p.ldo;
-        const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * dvr;
-        for (int c = lane; c < dvr; c += 32)
-          stf(orow + h * dvr + c, os[tt * dvp + c] * rstd * __bfloat162float(nwt[c]) / (1.f + expf(-ldf(grow + c))));
+        const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * dv;
+        for (int c = lane; c < dv; c += 32)
+          stf(orow + h * dv + c, os[tt * dvp + c] * rstd * __bfloat162float(nwt[c]) / (1.f + expf(-ldf(grow + c))));
         if (h == p.H - 1)
-          for (int64_t c = (int64_t)p.H * dvr + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+          for (int64_t c = (int64_t)p.H * dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
       }
     }
     if (MODE == MODE_DELTA && !p.y) {
@@ -290,7 +338,11 @@ __global__ void __launch_bounds__(RPT <= 4 ? 1024 : (RPT <= 32 ? 512 : 256), 1) 
       }
     }
   }
-  if (MODE == MODE_MLSTM && p.mstate && tid == 0 && blockIdx.z == 0) p.mstate[(int64_t)b * p.H + h] = mrun;
+  if (MODE == MODE_MLSTM && Sg && blockIdx.z == 0) {
+    __syncthreads();                                     // the last round's normaliser is complete
+    if (tid == 0) p.mstate[(int64_t)b * p.H + h] = mrun;
+    for (int e = tid; e < dk; e += nthr) Sg[(int64_t)dk * dv + e] = nvec[e];
+  }
   if (Sg) {
 #pragma unroll
     for (int c = 0; c < CPT; ++c)
@@ -325,26 +377,26 @@ __global__ void __launch_bounds__(256) delta_head_norm_kernel(ScanArgs p) {
     for (int64_t c = (int64_t)p.H * p.dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
 }
 
-// the same for the matrix memory's read-outs (rows, H, dv_real + 1) with e^{-m} beside them
+// the same for the matrix memory's read-outs (rows, H, dv) with the reciprocal denominators beside them
 template <typename T>
 __global__ void __launch_bounds__(256) mlstm_head_norm_kernel(ScanArgs p) {
   const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (wid >= (int64_t)p.B * p.L * p.H) return;
   const int64_t row = wid / p.H; const int h = (int)(wid % p.H);
-  const int dvr = p.dv_real;
-  const float* r = p.y + wid * p.dv;
-  const float inv = 1.f / (fmaxf(fabsf(r[dvr]), p.em[wid]) + p.den_eps);
+  const int dv = p.dv;
+  const float* r = p.y + wid * dv;
+  const float inv = p.em[wid];
   float ss = 0.f;
-  for (int c = lane; c < dvr; c += 32) { const float o = r[c] * inv; ss = fmaf(o, o, ss); }
+  for (int c = lane; c < dv; c += 32) { const float o = r[c] * inv; ss = fmaf(o, o, ss); }
   ss = warp_sum(ss);
-  const float rstd = inv / sqrtf(ss / (float)dvr + p.eps);
+  const float rstd = inv / sqrtf(ss / (float)dv + p.eps);
   T* orow = (T*)p.out + row * p.ldo;
-  const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * dvr;
-  const bf16* nw = (const bf16*)p.norm_w + (int64_t)h * dvr;
-  for (int c = lane; c < dvr; c += 32) stf(orow + h * dvr + c, r[c] * rstd * __bfloat162float(nw[c]) / (1.f + expf(-ldf(grow + c))));
+  const T* grow = (const T*)p.gate + row * p.ldg + (int64_t)h * dv;
+  const bf16* nw = (const bf16*)p.norm_w + (int64_t)h * dv;
+  for (int c = lane; c < dv; c += 32) stf(orow + h * dv + c, r[c] * rstd * __bfloat162float(nw[c]) / (1.f + expf(-ldf(grow + c))));
   if (h == p.H - 1)
-    for (int64_t c = (int64_t)p.H * dvr + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
+    for (int64_t c = (int64_t)p.H * dv + lane; c < p.ldo; c += 32) stf(orow + c, 0.f);
 }
 
 struct Plan { int rpt, lpc, dvc, chunks; };
@@ -371,7 +423,7 @@ inline Plan plan(int dk, int dv, int64_t ctas, int64_t L) {
 
 template <typename T, int RPT, int LPC, int MODE>
 int launch(const ScanArgs& a, const Plan& pl, cudaStream_t st, const char* what) {
-  const size_t smem = sizeof(float) * ((size_t)2 * TCH * LPC * RPT + (size_t)2 * TCH * pl.dvc + (size_t)TCH * 4);
+  const size_t smem = sizeof(float) * ((size_t)2 * TCH * LPC * RPT + (size_t)2 * TCH * pl.dvc + (size_t)TCH * 4 + (size_t)LPC * RPT + (size_t)TCH * TCH + TCH);
   auto kern = matrix_state_kernel<T, RPT, LPC, MODE>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<dim3(a.H, a.B, pl.chunks), dim3(LPC * pl.dvc / columns_per_thread(RPT)), smem, st>>>(a, pl.dvc);
@@ -457,14 +509,14 @@ inline ScanArgs mlstm_args(const evo_mlstm_params* p) {
   a.i_bias = p->i_bias; a.f_bias = p->f_bias; a.cap = p->cap; a.den_eps = p->den_eps; a.q_scale = p->q_scale;
   a.state = p->state; a.mstate = p->mstate; a.zero_start = p->zero_start;
   a.gate = p->gate; a.ldg = p->ld_gate; a.norm_w = p->norm_w; a.eps = p->eps; a.out = p->out; a.ldo = p->ldo;
-  a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->H; a.dk = p->dk; a.dv = p->dv + 1; a.dv_real = p->dv;
+  a.B = p->B; a.L = p->L; a.H = p->H; a.G = p->H; a.dk = p->dk; a.dv = p->dv;
   return a;
 }
 }  // namespace
 
 extern "C" size_t evo_mlstm_workspace(const evo_mlstm_params* p) {
-  const Plan pl = plan(p->dk, p->dv + 1, (int64_t)p->B * p->H, p->L);
-  return pl.chunks > 1 ? sizeof(float) * (size_t)p->B * p->L * p->H * (p->dv + 2) : 0;
+  const Plan pl = plan(p->dk, p->dv, (int64_t)p->B * p->H, p->L);
+  return pl.chunks > 1 ? sizeof(float) * (size_t)p->B * p->L * p->H * (p->dv + 1) : 0;
 }
 
 extern "C" int evo_mlstm_fwd(const evo_mlstm_params* p, void* workspace, size_t workspace_bytes, void* stream) {

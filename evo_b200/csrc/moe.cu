@@ -42,7 +42,7 @@ struct RouteArgs {
 
 template <typename T, bool VEC, int TOK>
 __global__ void __launch_bounds__(RW * 32) moe_route_kernel(const T* __restrict__ h, int64_t ldh, RouteArgs a) {
-  extern __shared__ float sm[];             // [TOK][2 E + n_extra + 2 groups]: scores (then the extra rows' logits), choice scores, group ranks, group flags
+  extern __shared__ float sm[];             // [TOK][2 E + n_extra + 2 groups]: scores (then the extra rows' logits), selection scores, group ranks, group flags
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int E = a.E, D = a.D, NL = E + a.n_extra, per_tok = 2 * E + a.n_extra + 2 * a.groups;
   const int64_t row0 = (int64_t)blockIdx.x * TOK;
@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(RW * 32) moe_route_kernel(const T* __restrict_
   for (int t = w; t < nt; t += RW) {
     float* s = sm + (size_t)t * per_tok;
     float* x = s + E;                        // extra rows' logits
-    float* c = x + a.n_extra;                // choice scores
+    float* c = x + a.n_extra;                // selection scores
     float* rank = c + E;                     // [groups]
     float* kept = rank + a.groups;           // [groups]
     const int64_t row = row0 + t;
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(RW * 32) moe_route_kernel(const T* __restrict_
     for (int e = lane; e < a.n_extra; e += 32) wrow[E + e] = 1.f / (1.f + expf(-x[e]));
     __syncwarp();
     if (a.groups > 1) {
-      // a run's rank: the sum of its two largest choice scores; the `keep` best runs stay, the others' experts cannot be chosen
+      // a run's rank: the sum of its two largest selection scores; the `keep` best runs stay, the others' experts cannot be chosen
       const int per = E / a.groups;
       for (int g = lane; g < a.groups; g += 32) {
         float b0 = -INFINITY, b1 = -INFINITY;

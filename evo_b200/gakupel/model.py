@@ -11,7 +11,7 @@ trace replay and command line drive it.  State, keyed by RUN index r:
     d["mha"].key_value_memory_dict[r]   (B, max_seqlen, G*dim + G*vdim): keys (normed, rotated), then values
     d["hyena"].fir_state_dict[r]        (B, taps-1, channels) fp32: the last inputs of the delta rule's short convolutions
     d["hyena"].state_dict[r]            (B, heads, dim, vdim) fp32: the delta rule's matrix state; for the matrix memory
-                                        (B, heads, dim, vdim + 1): its last column is the normaliser
+                                        (B, heads, dim, vdim + 1): per head the dim x vdim matrix, then the dim entries of the normaliser
     d["hyena"].state_dict[-(r+1)]       (B, heads) fp32: the matrix memory's running maximum
 Closing one sublayer and opening the next is ONE row kernel (evo_post_norm): it sums the sublayer's outputs, norms them into x, after a
 feed-forward files the layer's result and mixes the earlier ones, and emits x in the activation type for the next GEMM -- or, for the
@@ -202,7 +202,7 @@ class Gakupel(StreamDecoder):
                          B=B, L=L, H=s.heads, dk=s.dim, dv=s.vdim)
         nws = _lib.lib().evo_mlstm_workspace(C.byref(mp))
         ws = torch.empty(nws, dtype=torch.uint8, device=dev) if nws else None
-        self._record("mlstm", 4.0 * M * s.heads * s.dim * (s.vdim + 1), lambda: check(_lib.lib().evo_mlstm_fwd(C.byref(mp), ptr(ws), nws, self._stream()), "evo_mlstm_fwd"))
+        self._record("mlstm", 3.0 * M * s.heads * s.dim * s.vdim, lambda: check(_lib.lib().evo_mlstm_fwd(C.byref(mp), ptr(ws), nws, self._stream()), "evo_mlstm_fwd"))
         return self._linear(out, pk["right_out"], M), pk["right_out"].Np
 
     def _parallel(self, r, i, layer, h, B, L, ip, rec, off, pos_dev, fresh):

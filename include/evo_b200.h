@@ -615,7 +615,7 @@ int evo_post_norm(const evo_post_norm_params* p, void* stream);
  * the raw gate projections gi, gf (H):   i = cap tanh((gi + i_bias) / cap),  f = logsigmoid(cap tanh((gf + f_bias) / cap))   (cap <= 0: no cap)
  *   m' = max(f + m, i);  S <- e^{f + m - m'} S + e^{i - m'} k v^T;  n likewise with k;  o = S^T (q q_scale) / (max(|n . q q_scale|, e^{-m'}) + den_eps)
  *   out = o / sqrt(mean_c o^2 + eps) * norm_w[h*dv + c] * sigmoid(gate[h*dv + c])
- * state (B, H, dk, dv + 1) fp32: S with n as its last column; mstate (B, H) fp32: m (zero_start: both start at 0).
+ * state (B, H, dk * dv + dk) fp32: S (dk x dv), then n; mstate (B, H) fp32: m (zero_start: all start at 0).
  * workspace: evo_mlstm_workspace() bytes (0 unless a head's value channels are spread over several CTAs). */
 typedef struct {
   const void* q; const void* k; const void* v; int64_t ld;

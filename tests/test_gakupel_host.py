@@ -142,14 +142,14 @@ def test_oracle_router_keeps_groups_and_normalises():
     w = {"router": torch.zeros(8, D, dtype=F64), "correction": torch.tensor([0.9, 0.0, 0.0, 0.0, 0.5, 0.45, 0.3, 0.35], dtype=F64)}
     h = torch.zeros(1, D, dtype=F64)                        # every score is sigmoid(0) = 1/2; the corrections alone decide
     r = {"experts": 8, "top": 2, "scale": 3.0, "groups": {"count": 4, "keep": 1}}
-    # group sums of the two largest choice scores: (1.4+.5, 1.0, .5+.5+.95, .5+.5+.65) -> group 2 wins although expert 0 is the single best
+    # group sums of the two largest selection scores: (1.4+.5, 1.0, .5+.5+.95, .5+.5+.65) -> group 2 wins although expert 0 is the single best
     got = O.route(h, w, r)[0]
     assert got.nonzero().flatten().tolist() == [4, 5] and torch.allclose(got[[4, 5]], torch.tensor([1.5, 1.5], dtype=F64))
     r["groups"]["keep"] = 4
     assert O.route(h, w, r)[0].nonzero().flatten().tolist() == [0, 4]
     del r["groups"]
     assert O.route(h, w, r)[0].nonzero().flatten().tolist() == [0, 4]
-    # negative choice scores inside a kept group still beat every expert outside it
+    # negative selection scores inside a kept group still beat every expert outside it
     w["correction"] = torch.tensor([-3.0, -4.0, -0.9, -0.8, -0.7, -5.0, -0.6, -0.65], dtype=F64)
     r["groups"] = {"count": 4, "keep": 1}
     assert O.route(h, w, r)[0].nonzero().flatten().tolist() == [6, 7]

@@ -117,7 +117,7 @@ def test_post_norm_sums_norms_files_mixes_and_gathers(D, ldo, dtype):
     _close(xd, x.double() + O.layer_norm(scales[0] * ys[0][:, :D].double(), nw.double(), nb.double(), eps), 2e-6, "one input, no output")
 
 
-@pytest.mark.parametrize("H,G,dk,dv,rot,per_head,every", [(4, 2, 16, 16, 8, True, 0), (3, 1, 10, 9, 6, False, 4), (2, 2, 64, 48, 0, False, 256), (6, 3, 64, 64, 32, True, 0),
+@pytest.mark.parametrize("H,G,dk,dv,rot,per_head,every", [(4, 2, 16, 16, 8, True, 0), (3, 1, 10, 9, 6, False, 4), (2, 2, 64, 40, 0, False, 192), (6, 2, 64, 64, 16, True, 0),
                                                           (1, 1, 7, 5, 2, True, 1)])
 @pytest.mark.parametrize("dtype", [F32, B16])
 def test_qk_prep_head_norms_rotation_and_temperature(H, G, dk, dv, rot, per_head, every, dtype):
@@ -154,7 +154,7 @@ def test_qk_prep_head_norms_rotation_and_temperature(H, G, dk, dv, rot, per_head
     assert (cache[0, :pos0] == 0).all() and (cache[0, pos0 + L:] == 0).all()
 
 
-@pytest.mark.parametrize("E,top,groups,keep,extra,M", [(8, 3, 4, 2, 1, 37), (12, 2, 3, 2, 1, 1100), (6, 3, 3, 2, 0, 5), (16, 4, 0, 0, 1, 9), (64, 6, 8, 3, 1, 40), (5, 5, 5, 5, 0, 3),
+@pytest.mark.parametrize("E,top,groups,keep,extra,M", [(8, 3, 4, 2, 1, 37), (12, 3, 4, 2, 1, 1100), (6, 3, 3, 2, 0, 5), (16, 4, 0, 0, 1, 9), (64, 6, 8, 3, 1, 40), (5, 5, 5, 5, 0, 3),
                                                        (4, 1, 4, 1, 1, 2)])
 @pytest.mark.parametrize("dtype", [F32, B16])
 def test_router_scores_groups_choice_and_weights(E, top, groups, keep, extra, M, dtype):
@@ -173,7 +173,7 @@ def test_router_scores_groups_choice_and_weights(E, top, groups, keep, extra, M,
     p = MoeRouteParams(h=hd.data_ptr(), ldh=D, router_w=rwd.data_ptr(), correction=cd.data_ptr(), weights=out.data_ptr(), ldw=E + extra + 2, chosen=chosen.data_ptr(),
                        rows=M, D=D, E=E, top=top, n_extra=extra, score_fn=1, groups=groups, keep=keep, normalize=1, norm_eps=1e-20, scale=1.7, dtype=1 if dtype == F32 else 0)
     check(_lib.lib().evo_moe_route_ex(C.byref(p), _stream()))
-    # rows whose choice rests on a close call are left out (two choice scores, or two group ranks, within 1e-4)
+    # rows whose choice rests on a close call are left out (two selection scores, or two group ranks, within 1e-4)
     c = torch.sigmoid(h.double() @ rw[:E].double().T) + corr.double()
     srt = c.sort(-1).values
     safe = (srt[:, 1:] - srt[:, :-1]).min(-1).values > 1e-4
@@ -228,8 +228,8 @@ def _attention_reference(q, k, v, scale, r1, r2, sink, pos0):
     return out
 
 
-@pytest.mark.parametrize("H,G,dk,dv,biased,sink,L,pos0", [(4, 2, 64, 48, True, True, 200, 0), (2, 1, 16, 16, False, False, 150, 70), (3, 1, 10, 9, True, True, 90, 37),
-                                                        (6, 3, 64, 64, False, False, 130, 1), (2, 2, 128, 128, True, True, 70, 300)])
+@pytest.mark.parametrize("H,G,dk,dv,biased,sink,L,pos0", [(4, 2, 64, 40, True, True, 200, 0), (2, 1, 16, 16, False, False, 150, 70), (3, 1, 10, 9, True, True, 90, 37),
+                                                        (6, 2, 64, 64, False, False, 130, 1), (2, 2, 128, 128, True, True, 70, 300)])
 def test_attention_kernels_agree_with_bias_and_sink(H, G, dk, dv, biased, sink, L, pos0):
     """The many-query CUDA-core kernel (fp32), the tensor-core kernel (bf16, 16 rows or more) and the few-query kernel against fp64."""
     g = torch.Generator().manual_seed(H * dk + L)
@@ -273,7 +273,7 @@ def _one_layer(kind, T=70, seed=0, dtype=F32, mutate=None, **sizes):
 
 
 ATT_SIZES = [dict(att_heads=4, att_kv_heads=2, att_dim=16, rot_dims=8), dict(att_heads=3, att_kv_heads=1, att_dim=10, rot_dims=6, width=50),
-             dict(att_heads=6, att_kv_heads=3, att_dim=64, rot_dims=32, width=96), dict(att_heads=2, att_kv_heads=2, att_dim=24, rot_dims=24),
+             dict(att_heads=6, att_kv_heads=2, att_dim=64, rot_dims=16, width=96), dict(att_heads=2, att_kv_heads=2, att_dim=24, rot_dims=24),
              dict(att_heads=1, att_kv_heads=1, att_dim=8, rot_dims=0), dict(att_heads=2, att_kv_heads=1, att_dim=136, rot_dims=4, width=72)]
 
 
@@ -286,7 +286,7 @@ def test_key_valued_attention_mixer_matches_the_oracle(sizes):
 
 
 LEFT_SIZES = [dict(left_heads=4, left_kv_heads=2, left_dim=16, left_vdim=12, temp_every=8), dict(left_heads=3, left_kv_heads=1, left_dim=10, left_vdim=9, temp_every=3, width=50),
-              dict(left_heads=2, left_kv_heads=2, left_dim=64, left_vdim=48, temp_every=0), dict(left_heads=1, left_kv_heads=1, left_dim=8, left_vdim=140, temp_every=1, width=40)]
+              dict(left_heads=2, left_kv_heads=2, left_dim=64, left_vdim=40, temp_every=0), dict(left_heads=1, left_kv_heads=1, left_dim=8, left_vdim=140, temp_every=1, width=40)]
 
 
 @pytest.mark.parametrize("sizes", LEFT_SIZES, ids=lambda s: "h{left_heads}g{left_kv_heads}k{left_dim}v{left_vdim}e{temp_every}".format(**s))
@@ -298,7 +298,7 @@ def test_biased_sink_attention_side_matches_the_oracle(sizes):
 
 
 MEM_SIZES = [dict(mem_heads=2, mem_dim=12, mem_vdim=20, gate_cap=6.0), dict(mem_heads=3, mem_dim=5, mem_vdim=7, gate_cap=2.0, width=50),
-             dict(mem_heads=4, mem_dim=48, mem_vdim=48, gate_cap=12.0, width=96), dict(mem_heads=1, mem_dim=72, mem_vdim=136, gate_cap=15.0),
+             dict(mem_heads=4, mem_dim=48, mem_vdim=40, gate_cap=10.0, width=96), dict(mem_heads=1, mem_dim=72, mem_vdim=136, gate_cap=15.0),
              dict(mem_heads=1, mem_dim=1, mem_vdim=1, gate_cap=1.0), dict(mem_heads=2, mem_dim=130, mem_vdim=31, gate_cap=5.0)]
 
 
@@ -325,7 +325,7 @@ def test_matrix_memory_spread_over_several_ctas_on_a_long_prompt():
     _close(_portions(model, tokens, [280, 1, 1, 18]), want, 3e-5, "prompt, steps, portion")
 
 
-DELTA_SIZES = [dict(heads=4, kv_heads=2, dim=8, vdim=16, taps=3), dict(heads=3, kv_heads=1, dim=5, vdim=7, taps=2, width=50), dict(heads=6, kv_heads=6, dim=32, vdim=64, taps=4, width=96),
+DELTA_SIZES = [dict(heads=4, kv_heads=2, dim=8, vdim=16, taps=3), dict(heads=3, kv_heads=1, dim=5, vdim=7, taps=2, width=50), dict(heads=6, kv_heads=3, dim=32, vdim=64, taps=4, width=96),
                dict(heads=1, kv_heads=1, dim=8, vdim=8, taps=1)]
 
 
@@ -402,7 +402,7 @@ def test_query_temperature_steps_at_multiples_of_its_period():
 CONFIGS = {
     "mixed": dict(),
     "delta_first": dict(layers=("delta", "attention", "parallel", "delta", "parallel"), mlps=("moe", None, "dense", "dense", "moe"), width=72, vocab=257, rot_dims=16, temp_every=5,
-                        experts=12, top=2, groups=3, keep=2, kv_heads=4),
+                        experts=12, top=3, groups=4, keep=2, kv_heads=4),
     "bare": dict(layers=("parallel", "attention", "delta"), mlps=(None, "moe", None), rot_dims=0, temp_every=0, groups=0, shared_ff=0, taps=1, top=1),
     "ones": dict(layers=("attention", "parallel", "delta"), mlps=("moe", "moe", "dense"), att_heads=1, att_kv_heads=1, left_heads=1, left_kv_heads=1, mem_heads=1, heads=1, kv_heads=1,
                  experts=4, top=1, groups=4, keep=1, temp_every=1, left_scale=1.0, right_scale=1.0, router_scale=1.0),
@@ -415,6 +415,14 @@ CONFIGS = {
 }
 
 
+def _tolerance(cfg, W, tokens, want):
+    """Bound on the 32-bit model's distance from the fp64 oracle: three times what the oracle itself loses when it runs in 32-bit floats
+    (a deep stack can meet a nearly empty key or head output, whose norms then magnify the rounding), at least 3e-5 of the scale."""
+    own = ((O.forward(tokens, W, cfg, dtype=F32).double() - want).abs().max() / want.abs().max()).item()
+    assert own < 1e-4
+    return max(3e-5, 3 * own)
+
+
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_model_whole_steps_and_portions_match_the_oracle_in_fp32(name):
     cfg = O.make_config(**CONFIGS[name])
@@ -423,22 +431,23 @@ def test_model_whole_steps_and_portions_match_the_oracle_in_fp32(name):
     tokens = _tokens(cfg, T)
     streams = []
     want = O.forward(tokens, W, cfg, taps=streams)
+    tol = _tolerance(cfg, W, tokens, want)
     model = _model(cfg, W)
     model._tap = []
     got, _ = model(torch.tensor([tokens], device=DEV))
     assert len(model._tap) == len(streams)
     for r, (a, b) in enumerate(zip(model._tap, streams)):
-        _close(a, b, 3e-5, f"{name}: stream handed on by layer {r}")
+        _close(a, b, tol, f"{name}: stream handed on by layer {r}")
     model._tap = None
-    _close(got[0], want, 3e-5, f"{name}: whole")
-    _close(_portions(model, tokens, [1] * T), want, 3e-5, f"{name}: token by token from the first token")
-    _close(_portions(model, tokens, [40] + [1] * 35), want, 3e-5, f"{name}: prompt then steps")
-    _close(_portions(model, tokens, [2, 2, 3, 30, 1, 2, 17, 9, 2, 5, 2]), want, 3e-5, f"{name}: portions")
-    _close(_portions(model, tokens[:1], [1]), want[:1], 3e-5, f"{name}: a one-token sequence")
-    _close(_portions(model, tokens[:2], [2]), want[:2], 3e-5, f"{name}: a two-token sequence")
+    _close(got[0], want, tol, f"{name}: whole")
+    _close(_portions(model, tokens, [1] * T), want, tol, f"{name}: token by token from the first token")
+    _close(_portions(model, tokens, [40] + [1] * 35), want, tol, f"{name}: prompt then steps")
+    _close(_portions(model, tokens, [2, 2, 3, 30, 1, 2, 17, 9, 2, 5, 2]), want, tol, f"{name}: portions")
+    _close(_portions(model, tokens[:1], [1]), want[:1], tol, f"{name}: a one-token sequence")
+    _close(_portions(model, tokens[:2], [2]), want[:2], tol, f"{name}: a two-token sequence")
     model.moe_sparse_min_rows = 1                             # only the chosen experts, row by row, instead of all experts densely
     sparse, _ = model(torch.tensor([tokens], device=DEV))
-    _close(sparse[0], want, 3e-5, f"{name}: chosen experts only")
+    _close(sparse[0], want, tol, f"{name}: chosen experts only")
 
 
 def test_layers_with_their_own_sizes_and_a_cache_that_has_to_grow():
@@ -453,9 +462,7 @@ def test_layers_with_their_own_sizes_and_a_cache_that_has_to_grow():
     W = O.random_weights(cfg, seed=21)
     tokens = _tokens(cfg, 70, seed=8)
     want = O.forward(tokens, W, cfg)
-    # six layers deep, one delta layer meets a nearly empty key: the bound is three times what the oracle itself loses in 32-bit floats
-    tol = max(3e-5, 3 * ((O.forward(tokens, W, cfg, dtype=F32).double() - want).abs().max() / want.abs().max()).item())
-    assert tol < 3e-4
+    tol = _tolerance(cfg, W, tokens, want)               # six layers deep, one delta layer meets a nearly empty key
     model = _model(cfg, W)
     got, _ = model(torch.tensor([tokens], device=DEV))
     _close(got[0], want, tol, "whole")
