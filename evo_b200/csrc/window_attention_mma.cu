@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
       } else {
         if (t_lo > wi_hi) continue;
         if (windowed && wi_lo - t_hi >= p.window && t_lo >= p.keep_first) continue;
-        full = !biased && nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
+        full = nk == KT && t_hi <= wi_lo && (!windowed || wi_hi - t_lo < p.window || t_hi < p.keep_first);
       }
 
 #pragma unroll
@@ -172,11 +172,13 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
         // mask, running max / sum, probabilities
         float mx0 = -INFINITY, mx1 = -INFINITY;
         if (full) {                                    // every key of the tile is visible to every row of the warp: no mask
+          const int d0 = (int)(i0 - k0) - qc;          // distance of the row's first key column in the tile (the lower row is 8 further)
 #pragma unroll
           for (int n = 0; n < KT / 8; ++n) {
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-              const float s = capped ? cap_out * (1.f - __fdividef(2.f, ex2(Pm[0][n][c] * cap_in) + 1.f)) : Pm[0][n][c] * scale2;
+              float s = capped ? cap_out * (1.f - __fdividef(2.f, ex2(Pm[0][n][c] * cap_in) + 1.f)) : Pm[0][n][c] * scale2;
+              if (biased && !pooled) s = fmaf(-r1, __log2f(fmaf(r2, (float)(((c < 2) ? d0 : d0 + 8) - (n * 8 + (c & 1))), 1.f)), s);
               Pm[0][n][c] = s;
               if (c < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
             }
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
                              (pooled ? kj < ((c < 2) ? seen0 : seen1) : (kj <= i && (!windowed || i - kj < p.window || kj < p.keep_first)));
             const float sc = capped ? cap_out * (1.f - __fdividef(2.f, ex2(Pm[0][n][c] * cap_in) + 1.f)) : Pm[0][n][c] * scale2;
             float s = vis ? sc : -INFINITY;                                // base-2 exponent: exp(x) = 2^(x log2 e)
-            if (biased && vis && !pooled) s -= r1 * log2f(1.f + r2 * (float)(i - kj));
+            if (biased && vis && !pooled) s = fmaf(-r1, __log2f(fmaf(r2, (float)(i - kj), 1.f)), s);
             Pm[0][n][c] = s;
             if (c < 2) mx0 = fmaxf(mx0, s); else mx1 = fmaxf(mx1, s);
           }
