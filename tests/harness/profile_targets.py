@@ -109,4 +109,29 @@ elif what in ("nelovik", "nelovik_step"):
             d["mha"].seqlen_offset = d["hyena"].seqlen_offset = ctx + t
             lg, _ = model(nxt, inference_params_dict=d)
     torch.cuda.synchronize()
+elif what in ("gakupel", "gakupel_step"):
+    # a 2-layer Gakupel model (biased sink attention beside a matrix memory; key-valued attention; one dense and one expert feed-forward) at
+    # width 2048: one prompt of 2 x 4096 tokens ("gakupel": every prompt kernel once per forward) or single-token steps of 16 sequences
+    from evo_b200.gakupel import Gakupel, GakupelConfig
+    moe = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": 1408}}
+    par = {"type": "parallel", "mlp": moe, "mixer": {
+        "left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.25, "every": 512}}, "left_scale": 1.0,
+        "right": {"heads": 16, "dim": 128, "vdim": 128, "gate_cap": 15.0}, "right_scale": 1.0}}
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": 5632},
+           "mixer": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 10000.0}}}
+    gc = {"architecture": "Gakupel", "vocab": 512, "width": 2048, "norm": {"eps": 1e-5}, "layers": [par, att]}
+    model = Gakupel(GakupelConfig.from_dict(gc)).init_random(0, device=dev)
+    if what == "gakupel":
+        ids = torch.randint(0, 512, (2, 4096), device=dev)
+        for _ in range(2):
+            model(ids)
+    else:
+        B, ctx = 16, 2048
+        d = model.initialize_inference_params(max_seqlen=ctx + 64, max_batch_size=B)
+        lg, d = model(torch.randint(0, 512, (B, ctx), device=dev), inference_params_dict=d)
+        nxt = lg[:, -1].argmax(-1, keepdim=True)
+        for t in range(3):
+            d["mha"].seqlen_offset = d["hyena"].seqlen_offset = ctx + t
+            lg, _ = model(nxt, inference_params_dict=d)
+    torch.cuda.synchronize()
 print("done", what)
