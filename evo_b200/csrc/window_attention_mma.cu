@@ -26,13 +26,20 @@ namespace {
 
 constexpr int WARPS = 4, QROWS = 16, KT = 64;
 
+// 16 bytes global -> shared without passing through registers; !live: 16 zero bytes (nothing is read)
+__device__ __forceinline__ void copy16_async(void* dst, const void* src, bool live) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(live ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // NV8 = padded dv / 8 (output tiles of 8 channels per warp row block)
 template <int NV8, int NM>
-__global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_attn_params p, int dkp, int qst, int kst, int vst, int vec, int2 vstep) {
+__global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_attn_params p, int dkp, int qst, int kst, int vst, int vec, int2 vstep, int nbuf) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [WARPS*16][qst]   both maps' queries
-  bf16* Ks = Qs + WARPS * QROWS * qst;                           // [KT][kst]         both maps' keys
-  bf16* Vs = Ks + KT * kst;                                      // [KT][vst]         values
+  bf16* Ks0 = Qs + WARPS * QROWS * qst;                          // [nbuf][KT][kst]   both maps' keys
+  bf16* Vs0 = Ks0 + nbuf * KT * kst;                             // [nbuf][KT][vst]   values
   const int dk = p.dk, dv = p.dv;
   const int b = blockIdx.z, h = blockIdx.y, g = h / (p.H / p.G);
   const int tid = threadIdx.x, w = tid >> 5, lane = tid & 31, qr = lane >> 2, qc = (lane & 3) * 2;
@@ -97,30 +104,43 @@ __global__ void __launch_bounds__(WARPS * 32) window_attn_mma_kernel(evo_window_
   const bool biased = p.dist_r1 != nullptr;
   const float r1 = biased ? __bfloat162float(((const bf16*)p.dist_r1)[h]) : 0.f, r2 = biased ? __bfloat162float(((const bf16*)p.dist_r2)[h]) : 0.f;
 
+  int cur = 0;                                          // buffer of the tile in work
   for (int part = 0; part < 3; ++part) {               // kept first tokens, pooled blocks, window
     const int64_t lo = part == 2 ? win_lo : 0, hi = part == 0 ? keep_hi : (part == 1 ? pool_hi : i_hi + 1);
     const bool pooled = part == 1;
     const bf16* kbase = pooled ? pkb : kb;
     const bf16* vbase = pooled ? pvb : vb;
     const int64_t kstr = pooled ? p.pool_tok_stride : p.k_tok_stride, vstr = pooled ? p.pool_tok_stride : p.v_tok_stride;
+    // the tile that starts at key t0, as asynchronous 16-byte copies into buffer `bufi` (one group per thread)
+    const auto fetch = [&](int64_t t0, int bufi) {
+      const int n = (int)min((int64_t)KT, hi - t0);
+      bf16* Kd = Ks0 + bufi * KT * kst;
+      bf16* Vd = Vs0 + bufi * KT * vst;
+      for (int r = vr0, cc = vc0; r < KT; ) {
+        const int m = cc >= cpm, e = (cc - m * cpm) * 8;
+        const bool live = r < n && e < dk;
+        copy16_async(Kd + r * kst + cc * 8, live ? kbase + (t0 + r) * kstr + m * dk + e : kbase, live);
+        r += vstep.x; cc += vstep.y;
+        if (cc >= c8n) { cc -= c8n; ++r; }
+      }
+      for (int idx = tid; idx < KT * NV8; idx += WARPS * 32) {
+        const int r = idx / NV8, c = (idx % NV8) * 8;
+        const bool live = r < n && c < dv;
+        copy16_async(Vd + r * vst + c, live ? vbase + (t0 + r) * vstr + c : vbase, live);
+      }
+      copies_commit();
+    };
+    bool ahead = false;                                // the tile of this iteration was fetched during the previous one
     for (int64_t k0 = lo; k0 < hi; k0 += KT) {
       const int nk = (int)min((int64_t)KT, hi - k0);
-      __syncthreads();
+      bf16* Ks = Ks0 + cur * KT * kst;
+      bf16* Vs = Vs0 + cur * KT * vst;
+      __syncthreads();                                 // every warp has left the previous tile: the other buffer may be overwritten
       if (vec) {
-        for (int r = vr0, cc = vc0; r < KT; ) {
-          const int m = cc >= cpm, e = (cc - m * cpm) * 8;
-          uint4 v = zero4;
-          if (r < nk && e < dk) v = *reinterpret_cast<const uint4*>(kbase + (k0 + r) * kstr + m * dk + e);
-          *reinterpret_cast<uint4*>(Ks + r * kst + cc * 8) = v;
-          r += vstep.x; cc += vstep.y;
-          if (cc >= c8n) { cc -= c8n; ++r; }
-        }
-        for (int idx = tid; idx < KT * NV8; idx += WARPS * 32) {
-          const int r = idx / NV8, c = (idx % NV8) * 8;
-          uint4 v = zero4;
-          if (r < nk && c < dv) v = *reinterpret_cast<const uint4*>(vbase + (k0 + r) * vstr + c);
-          *reinterpret_cast<uint4*>(Vs + r * vst + c) = v;
-        }
+        if (!ahead) fetch(k0, cur);
+        if (nbuf == 2 && k0 + KT < hi) { fetch(k0 + KT, cur ^ 1); ahead = true; copies_wait<1>(); }
+        else { ahead = false; copies_wait<0>(); }
+        if (nbuf == 2) cur ^= 1;
       } else {
         for (int idx = tid; idx < KT * NM * dkp; idx += WARPS * 32) {
           const int r = idx / (NM * dkp), c = idx % (NM * dkp), m = c / dkp, e = c % dkp;
@@ -300,16 +320,19 @@ template <int NV8, int NM>
 int launch(const evo_window_attn_params* p, cudaStream_t st) {
   const int dkp = (p->dk + 15) / 16 * 16;
   const int qst = NM * dkp + 8, kst = NM * dkp + 8, vst = NV8 * 8 + 8;
-  const size_t smem = sizeof(bf16) * ((size_t)WARPS * QROWS * qst + (size_t)KT * kst + (size_t)KT * vst);
+  // two K/V buffers (the next tile is fetched while the current one is in work) as long as two CTAs still fit an SM's shared memory
+  const size_t tile = sizeof(bf16) * ((size_t)KT * kst + (size_t)KT * vst), qbytes = sizeof(bf16) * (size_t)WARPS * QROWS * qst;
   auto a16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
   const int vec = p->dk % 8 == 0 && p->dv % 8 == 0 && p->q_tok_stride % 8 == 0 && p->k_tok_stride % 8 == 0 && p->v_tok_stride % 8 == 0 &&
                   p->k_batch_stride % 8 == 0 && p->v_batch_stride % 8 == 0 && a16(p->q) && a16(p->k) && a16(p->v) &&
                   (p->pool <= 0 || (p->pool_tok_stride % 8 == 0 && p->pool_batch_stride % 8 == 0 && a16(p->pool_k) && a16(p->pool_v)));
+  const int nbuf = vec && qbytes + 2 * tile <= 110 * 1024 ? 2 : 1;
+  const size_t smem = qbytes + nbuf * tile;
   auto kern = window_attn_mma_kernel<NV8, NM>;
   if (smem > 48 * 1024) EVO_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int c8n = NM * dkp / 8;
   kern<<<dim3((unsigned)((p->Lq + WARPS * QROWS - 1) / (WARPS * QROWS)), p->H, p->B), WARPS * 32, smem, st>>>(*p, dkp, qst, kst, vst, vec,
-                                                                                                                 make_int2(WARPS * 32 / c8n, WARPS * 32 % c8n));
+                                                                                                                 make_int2(WARPS * 32 / c8n, WARPS * 32 % c8n), nbuf);
   return check_launch("evo_window_attn_fwd");
 }
 
