@@ -24,6 +24,7 @@
 // for itself, so a head spread over several CTAs needs no exchange.
 // The single-token step is the same kernel with L == 1.
 #include "common.cuh"
+#include <stdlib.h>
 #include "../../include/evo_b200.h"
 #include <math.h>
 #include <algorithm>
@@ -407,6 +408,10 @@ inline int columns_per_thread(int rpt) { return rpt <= 16 ? 2 : 1; }
 inline Plan plan(int dk, int dv, int64_t ctas, int64_t L) {
   int rpt = 4;
   while (rpt < 64 && rpt * 8 < dk) rpt <<= 1;
+  // prompts on so few (head, sequence) pairs that every CTA of 512 threads gets an SM of its own: 16 lanes per column with half the rows
+  // each (one more shuffle step per fold) put twice the warps on an SM.  EVO_B200_MATRIX_STATE_LANES = 8 | 16 fixes the choice (comparisons).
+  static const int forced = [] { const char* e = getenv("EVO_B200_MATRIX_STATE_LANES"); return e ? atoi(e) : 0; }();
+  if (rpt == 16 && L >= 256 && forced != 8 && (forced == 16 || ctas * ((dv + 63) / 64) <= device_sm_count())) rpt = 8;
   int lpc = 1;
   while (lpc * rpt < dk) lpc <<= 1;
   if (lpc > 32) return {0, 0, 0, 0};
@@ -453,6 +458,7 @@ int dispatch(ScanArgs a, void* workspace, size_t workspace_bytes, cudaStream_t s
     case 404: return launch<T, 4, 4, MODE>(a, pl, st, what);
     case 408: return launch<T, 4, 8, MODE>(a, pl, st, what);
     case 808: return launch<T, 8, 8, MODE>(a, pl, st, what);
+    case 816: return launch<T, 8, 16, MODE>(a, pl, st, what);
     case 1608: return launch<T, 16, 8, MODE>(a, pl, st, what);
     case 3208: return launch<T, 32, 8, MODE>(a, pl, st, what);
     case 6408: return launch<T, 64, 8, MODE>(a, pl, st, what);

@@ -325,6 +325,18 @@ def test_matrix_memory_spread_over_several_ctas_on_a_long_prompt():
     _close(_portions(model, tokens, [280, 1, 1, 18]), want, 3e-5, "prompt, steps, portion")
 
 
+@pytest.mark.parametrize("kind,sizes", [("delta", dict(heads=2, kv_heads=1, dim=128, vdim=72, taps=2)), ("delta", dict(heads=3, kv_heads=3, dim=66, vdim=6, taps=3)),
+                                        ("parallel", dict(mem_heads=2, mem_dim=100, mem_vdim=130, left_scale=0.0)), ("parallel", dict(mem_heads=1, mem_dim=128, mem_vdim=64, left_scale=0.0))])
+def test_recurrences_with_sixteen_lanes_per_column_on_a_long_prompt(kind, sizes):
+    """Prompts of 256 tokens or more on few heads of 65 to 128 state rows put 16 lanes on a state column instead of 8; the portions behind the
+    prompt run with 8 lanes on the state it left."""
+    cfg, W, tokens, want, model = _one_layer(kind, T=300, seed=4, width=48, **sizes)
+    got, _ = model(torch.tensor([tokens], device=DEV))
+    _close(got[0], want, 3e-5, "whole")
+    _close(_portions(model, tokens, [270, 1, 1, 28]), want, 3e-5, "prompt, steps, portion")
+    _close(_portions(model, tokens, [12, 260, 28]), want, 3e-5, "a long portion on a carried state")
+
+
 DELTA_SIZES = [dict(heads=4, kv_heads=2, dim=8, vdim=16, taps=3), dict(heads=3, kv_heads=1, dim=5, vdim=7, taps=2, width=50), dict(heads=6, kv_heads=3, dim=32, vdim=64, taps=4, width=96),
                dict(heads=1, kv_heads=1, dim=8, vdim=8, taps=1)]
 

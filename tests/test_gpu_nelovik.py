@@ -218,6 +218,18 @@ def test_state_space_mixer_matches_the_oracle(sizes):
     _close(_portions(model, tokens, [17, 2, 1, 16, 2, 7]), want, 2e-5, "portions")
 
 
+def test_state_space_mixer_with_sixteen_lanes_per_column_on_a_long_prompt():
+    """Prompts of 256 tokens or more on few heads of 65 to 128 state rows put 16 lanes on a state column; shorter portions continue with 8."""
+    cfg = O.make_config(layers=("parallel",), no_ff_layers=(0,), width=40, ssd_heads=2, ssd_vdim=40, state=128, groups=1, norm_groups=2, ssd_taps=2)
+    W = _one_side(O.random_weights(cfg, seed=17), "right")
+    tokens = _tokens(cfg, 300)
+    want = O.forward(cfg, W, tokens)
+    model = _model(cfg, W)
+    got, _ = model(torch.tensor([tokens], device=DEV))
+    _close(got[0], want, 2e-5, "whole")
+    _close(_portions(model, tokens, [12, 260, 1, 27]), want, 2e-5, "a long portion on a carried state, a step, a portion")
+
+
 ATT_SIZES = [dict(att_heads=4, att_kv_heads=2, att_dim=12, att_vdim=10, window=9, pool=3, rot_dims=8), dict(att_heads=3, att_kv_heads=3, att_dim=16, att_vdim=16, window=7, pool=4, rot_dims=16),
              dict(att_heads=2, att_kv_heads=1, att_dim=40, att_vdim=136, window=33, pool=1, rot_dims=0), dict(att_heads=5, att_kv_heads=1, att_dim=6, att_vdim=3, window=1, pool=2, rot_dims=2),
              dict(att_heads=2, att_kv_heads=2, att_dim=8, att_vdim=8, window=200, pool=5, rot_dims=4), dict(att_heads=2, att_kv_heads=2, att_dim=24, att_vdim=8, window=12, pool=0, rot_dims=6, softcap=0.0)]
