@@ -13,6 +13,8 @@
 // barrier.  Value channels are independent in both recurrences: a head whose state does not fit one CTA's registers, or a call
 // that would leave SMs idle, is spread over several CTAs by value channel; the delta rule's read-outs then go to an fp32
 // workspace and a second small kernel applies the head norm, weight and gate.
+// Prompts on so few (head, sequence) pairs that every CTA has an SM of its own put 16 lanes with half the rows on a column of 65 to 128 rows
+// (twice the warps per SM for one more shuffle step per fold).
 // TCH tokens are staged per round in shared memory: (k, q) pairs per state row, values, and the per-token numbers.
 // The delta rule needs S^T k before it can write: both products are taken from the decayed state in one pass,
 //   p = (gS)^T k,  r = (gS)^T q,  u = beta (v - p),  o = r + u (k . q),

@@ -5,7 +5,8 @@
 //
 // CTA = 4 warps x 16 queries, 64-key tiles of K (both maps) and V in shared memory as bf16, row-major with 16-byte row padding
 // (conflict-free fragment reads; V fragments come transposed out of ldmatrix), filled with 16-byte copies when the head sizes and
-// strides are multiples of 8.  A warp keeps both maps' output accumulators (16 x dv fp32 each) in registers and handles one map
+// strides are multiples of 8 -- asynchronous ones into two buffers, the next tile on its way while the current one is in work, as
+// long as two CTAs still fit an SM's shared memory.  A warp keeps both maps' output accumulators (16 x dv fp32 each) in registers and handles one map
 // at a time (scores -> softmax -> P.V), so only one 16 x 64 tile of probabilities is live.
 // Head sizes are padded to 16 in shared memory (zero columns); dk <= 128, dv <= 128 and dv % 8 == 0, otherwise the CUDA-core
 // kernel runs.  The tile walk is the CUDA-core kernel's: [0, keep_first), the pooled blocks that the CTA's last query sees, and the
